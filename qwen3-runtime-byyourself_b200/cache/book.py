@@ -35,7 +35,8 @@ class CacheNeed:
     a fixed-size float32 area per sequence (empty: none); it can go with any kind.
     `value_dim` is the size of a value row where it differs from the key's `head_dim`;
     `value_heads` the number of value heads where it differs from `num_kv_heads` (values
-    that several key heads share).
+    that several key heads share).  `block_state` is a second float32 area per sequence, of that many values, for
+    what the layer's block keeps from token to token beside its mixer's state (empty: 0).
     """
     kind: str = "none"
     num_kv_heads: int = 0
@@ -44,6 +45,7 @@ class CacheNeed:
     state_shape: Tuple[int, ...] = ()
     value_dim: Optional[int] = None
     value_heads: Optional[int] = None
+    block_state: int = 0
 
     def __post_init__(self):
         if self.kind not in ("full", "window", "chunk", "none"):
@@ -168,6 +170,7 @@ class CacheBook:
         self.page_tokens = PAGE_TOKENS
         self.group_of_layer: Dict[int, int] = {}
         self.state_layers: Dict[int, Tuple[int, ...]] = {}
+        self.block_state_layers: Dict[int, int] = {}
         by_key: Dict[tuple, int] = {}
         group_needs: List[CacheNeed] = []
         group_layers: List[List[int]] = []
@@ -176,6 +179,8 @@ class CacheBook:
                 continue
             if need.state_shape:
                 self.state_layers[layer] = tuple(need.state_shape)
+            if need.block_state:
+                self.block_state_layers[layer] = int(need.block_state)
             if need.kind == "none":
                 continue
             key = need.group_key()

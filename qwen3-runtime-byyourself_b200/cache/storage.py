@@ -6,7 +6,8 @@ the keys and one, [..., value_dim], for the values.
 A (page, kv head) tile is one contiguous [PAGE_TOKENS, head_dim] panel, so a kernel
 streams whole panels and a 2-D bulk copy can fetch one.  State rows are float32
 [slot, *state_shape] per layer and are zeroed when the slot is handed out; row number
-`n_slots` belongs to no sequence and takes the padding rows of a fixed-size decode batch.  Every group
+`n_slots` belongs to no sequence and takes the padding rows of a fixed-size decode batch; a layer's block may keep
+a second such area (`block_state`, [slot, n]).  Every group
 has one page more than its pool hands out: page number `n_pages` belongs to no
 sequence and takes the writes of the padding rows of a fixed-size decode batch.
 """
@@ -30,6 +31,7 @@ class LayerCache:
     state: Optional[torch.Tensor]     # [n_slots, *state_shape] float32
     window: Optional[int] = None
     shared: bool = False              # the view of a layer that reads another layer's cache: it must not write
+    block_state: Optional[torch.Tensor] = None   # [n_slots + 1, n] float32: what the layer's block keeps per sequence
 
 
 class KVCache(CacheBook):
@@ -49,6 +51,8 @@ class KVCache(CacheBook):
                                                 device=self.device)))
         self.states = {layer: torch.zeros((self.n_slots + 1,) + shape, dtype=torch.float32, device=self.device)
                        for layer, shape in self.state_layers.items()}
+        self.block_states = {layer: torch.zeros((self.n_slots + 1, n), dtype=torch.float32, device=self.device)
+                             for layer, n in self.block_state_layers.items()}
         self._views: Dict[int, LayerCache] = {}
         for layer, need in enumerate(needs):
             if need is None:
@@ -60,12 +64,13 @@ class KVCache(CacheBook):
                 store = self.stores[gi]
                 keys, values = (store[0][li], store[1][li]) if isinstance(store, tuple) else (store[li, 0], store[li, 1])
             self._views[layer] = LayerCache(gi, keys, values, self.states.get(layer),
-                                            need.window if need.kind == "window" else None)
+                                            need.window if need.kind == "window" else None,
+                                            block_state=self.block_states.get(layer))
         for layer, src in (cache_from or {}).items():
             self._views[layer] = dataclasses.replace(self._views[src], shared=True)
 
     def _on_alloc(self, slot: int) -> None:
-        for state in self.states.values():
+        for state in list(self.states.values()) + list(self.block_states.values()):
             state[slot].zero_()
 
     def layer(self, index: int) -> LayerCache:

@@ -5,6 +5,8 @@ from .registry import (ConfigError, config_class_for, config_from_dict, known_ar
 from .qwen3 import Qwen3Config
 from .dozazen import DozazenConfig
 from .lagulorn import LagulornConfig
+from .fagunex import FagunexConfig
 
 __all__ = ["LayerSpec", "ModelPlan", "PartSpec", "StreamStep", "ConfigError", "config_class_for", "config_from_dict",
-           "known_architectures", "load_config", "register_architecture", "Qwen3Config", "DozazenConfig", "LagulornConfig"]
+           "known_architectures", "load_config", "register_architecture", "Qwen3Config", "DozazenConfig", "LagulornConfig",
+           "FagunexConfig"]

@@ -28,6 +28,7 @@ namespace {
 
 constexpr int PAGE = Q3_PAGE_TOKENS;
 constexpr int MAX_HEAD_DIM = 256;
+constexpr int GENERIC_KEY_DIM = 1024, GENERIC_VALUE_DIM = 512;   // what the general attention kernel takes
 
 template <typename T> __device__ __forceinline__ void load_pack_f32(const T* p, float (&v)[Pack<T>::N]) {
     const Pack<T> k = load_pack<T>(p);
@@ -235,14 +236,16 @@ __global__ void qkv_prepare_vec_kernel(const T* __restrict__ qkv, T* __restrict_
 }
 
 // One block per (query head, token).  128 threads: the four warps share the keys of a
-// page for the scores; thread t owns output dims t and t + 128.
+// page for the scores; thread t owns output dims t, t + 128, t + 256 and t + 384.  Keys up to GENERIC_KEY_DIM and
+// values up to GENERIC_VALUE_DIM wide: the rows of a latent cache (one wide key/value head for all query heads).
 template <typename T>
 __global__ void __launch_bounds__(128)
 attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                          T* __restrict__ out, const int* __restrict__ token_seq, const int* __restrict__ token_pos,
                          const int* __restrict__ page_table, int pages_per_seq, int nq, int nkv, int d, float scale,
-                         int window, int vd, float softcap, int chunk, int sink, int nv, int out_f32) {
-    __shared__ float q_s[MAX_HEAD_DIM];
+                         int window, int vd, float softcap, int chunk, int sink, int nv, int out_f32,
+                         const float* __restrict__ sink_values) {
+    __shared__ float q_s[GENERIC_KEY_DIM];
     __shared__ float score[PAGE];
     __shared__ float prob[PAGE];
     pdl_launch_dependents();
@@ -257,8 +260,10 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
     __syncthreads();
 
     const int lo = window > 0 ? max(0, pos - window + 1) : (chunk > 0 ? pos / chunk * chunk : 0);
-    // the sink is a key of score 0 without a value: the running maximum and sum start from it
-    float m_run = sink ? 0.0f : -INFINITY, l_run = sink ? 1.0f : 0.0f, acc0 = 0.0f, acc1 = 0.0f;
+    // the sink is a key without a value whose score is 0, or the head's own number (`sink_values`), neither scaled
+    // nor capped: the running maximum and sum start from it
+    float m_run = sink ? (sink_values ? sink_values[head] : 0.0f) : -INFINITY, l_run = sink ? 1.0f : 0.0f;
+    float acc[GENERIC_VALUE_DIM / 128] = {};
     const float inv_cap = softcap > 0.0f ? 1.0f / softcap : 0.0f;
     for (int pg = lo / PAGE; pg <= pos / PAGE; ++pg) {
         const T* kp = k_pages + ((int64_t)pages[pg] * nkv + kvh) * PAGE * d;
@@ -279,28 +284,31 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
         if (tid < PAGE) prob[tid] = (tid >= j_lo && tid <= j_hi) ? expf(score[tid] - m_new) : 0.0f;
         __syncthreads();
         const float alpha = expf(m_run - m_new);  // 0 on the first page (m_run = -inf, m_new finite)
-        float l_add = 0.0f, v0 = 0.0f, v1 = 0.0f;
+        float l_add = 0.0f, v_add[GENERIC_VALUE_DIM / 128] = {};
         for (int j = j_lo; j <= j_hi; ++j) {
             const float p = prob[j];
             l_add += p;
-            if (tid < vd) v0 = fmaf(p, to_f32<T>(vp[(int64_t)j * vd + tid]), v0);
-            if (tid + 128 < vd) v1 = fmaf(p, to_f32<T>(vp[(int64_t)j * vd + tid + 128]), v1);
+#pragma unroll
+            for (int n = 0; n < GENERIC_VALUE_DIM / 128; ++n)
+                if (tid + n * 128 < vd) v_add[n] = fmaf(p, to_f32<T>(vp[(int64_t)j * vd + tid + n * 128]), v_add[n]);
         }
         l_run = l_run * alpha + l_add;
-        acc0 = acc0 * alpha + v0;
-        acc1 = acc1 * alpha + v1;
+#pragma unroll
+        for (int n = 0; n < GENERIC_VALUE_DIM / 128; ++n) acc[n] = acc[n] * alpha + v_add[n];
         m_run = m_new;
         __syncthreads();  // score/prob are rewritten by the next page
     }
     if (out_f32) {                                   // the caller goes on in 32-bit (differences of attention maps)
         float* o = reinterpret_cast<float*>(out) + (t * nq + head) * (int64_t)vd;
-        if (tid < vd) o[tid] = acc0 / l_run;
-        if (tid + 128 < vd) o[tid + 128] = acc1 / l_run;
+#pragma unroll
+        for (int n = 0; n < GENERIC_VALUE_DIM / 128; ++n)
+            if (tid + n * 128 < vd) o[tid + n * 128] = acc[n] / l_run;
         return;
     }
     T* o = out + (t * nq + head) * (int64_t)vd;
-    if (tid < vd) o[tid] = from_f32<T>(acc0 / l_run);
-    if (tid + 128 < vd) o[tid + 128] = from_f32<T>(acc1 / l_run);
+#pragma unroll
+    for (int n = 0; n < GENERIC_VALUE_DIM / 128; ++n)
+        if (tid + n * 128 < vd) o[tid + n * 128] = from_f32<T>(acc[n] / l_run);
 }
 
 template <typename T>
@@ -339,17 +347,17 @@ template <typename T>
 int attention_generic_launch(const T* q, const T* k_pages, const T* v_pages, T* out, const int* token_seq,
                              const int* token_pos, const int* page_table, int pages_per_seq, int64_t n_tokens, int nq,
                              int nkv, int d, float scale, int window, int vd, float softcap, int chunk, int sink, int nv,
-                             int out_f32, cudaStream_t stream) {
+                             int out_f32, const float* sink_values, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (vd <= 0) vd = d;
     if (nv <= 0) nv = nkv;
     if (nkv <= 0 || nkv % nv != 0) return Q3_ERR_BAD_SIZE;
-    if (d <= 0 || d > MAX_HEAD_DIM || vd > MAX_HEAD_DIM || nq <= 0 || nkv <= 0 || nq % nkv != 0) return Q3_ERR_BAD_SIZE;
+    if (d <= 0 || d > GENERIC_KEY_DIM || vd > GENERIC_VALUE_DIM || nq <= 0 || nkv <= 0 || nq % nkv != 0) return Q3_ERR_BAD_SIZE;
     if (window > 0 && chunk > 0) return Q3_ERR_BAD_SIZE;
     if (n_tokens > 65535) return Q3_ERR_TOO_LARGE;
     const dim3 grid(nq, (unsigned)n_tokens);
     return (int)q3_launch(attention_generic_kernel<T>, grid, dim3(128), 0, stream, q, k_pages, v_pages, out, token_seq,
-                          token_pos, page_table, pages_per_seq, nq, nkv, d, scale, window, vd, softcap, chunk, sink, nv, out_f32);
+                          token_pos, page_table, pages_per_seq, nq, nkv, d, scale, window, vd, softcap, chunk, sink, nv, out_f32, sink_values);
 }
 
 }  // namespace
@@ -369,10 +377,11 @@ int attention_generic_launch(const T* q, const T* k_pages, const T* v_pages, T* 
                                                 const int* token_seq, const int* token_pos, const int* page_table,    \
                                                 int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d,          \
                                                 float scale, int window, int value_dim, float softcap,     \
-                                                int chunk, int sink, int value_heads, int out_f32, void* stream) {    \
+                                                int chunk, int sink, int value_heads, int out_f32,                   \
+                                                const float* sink_values, void* stream) {                             \
         return attention_generic_launch<T>((const T*)q, (const T*)k_pages, (const T*)v_pages, (T*)out, token_seq,     \
                                            token_pos, page_table, pages_per_seq, n_tokens, nq, nkv, d, scale, window, \
-                                           value_dim, softcap, chunk, sink, value_heads, out_f32,                     \
+                                           value_dim, softcap, chunk, sink, value_heads, out_f32, sink_values,        \
                                            (cudaStream_t)stream);                                                     \
     }
 

@@ -121,7 +121,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 prefill_capped_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                       TO* __restrict__ out, const int* __restrict__ seq_start, const int* __restrict__ seq_pos0,
                       const int* __restrict__ page_table, int pages_per_seq, int nq, int nkv, float scale, float cap, int chunk,
-                      int sink, int nv) {
+                      int sink, int nv, const float* __restrict__ sink_values) {
     extern __shared__ __align__(16) unsigned char smem[];
     pdl_launch_dependents();
     pdl_wait();
@@ -155,7 +155,7 @@ prefill_capped_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pag
     float o[NT][4];
 #pragma unroll
     for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
-    const float m0 = sink ? 0.0f : -INFINITY, l0 = sink ? 1.0f : 0.0f;
+    const float m0 = sink ? (sink_values ? sink_values[head] * LOG2E : 0.0f) : -INFINITY, l0 = sink ? 1.0f : 0.0f;   // base-2 scale
     float m_run[2] = {m0, m0}, l_run[2] = {l0, l0};
 
     const int last_row = min(tile * BM + BM, n_new) - 1;
@@ -536,15 +536,17 @@ decode_capped_split_kernel(const bf16* __restrict__ q, const bf16* k_pages, cons
 
 // One block per (query head, token): the splits' partial results, the sink, the division.
 template <typename TO>
-__global__ void decode_capped_merge_kernel(const float* __restrict__ part, TO* __restrict__ out, int nq, int n_splits, int sink) {
+__global__ void decode_capped_merge_kernel(const float* __restrict__ part, TO* __restrict__ out, int nq, int n_splits, int sink,
+                                           const float* __restrict__ sink_values) {
     pdl_launch_dependents();
     pdl_wait();
     const int head = blockIdx.x;
     const int64_t t = blockIdx.y;
     const float* p = part + ((t * nq + head) * n_splits) * (VD + 2);
-    float m = sink ? 0.0f : -INFINITY;
+    const float sink_score = sink_values ? sink_values[head] * LOG2E : 0.0f;     // base-2 scale, as the splits' maxima
+    float m = sink ? sink_score : -INFINITY;
     for (int s = 0; s < n_splits; ++s) m = fmaxf(m, p[s * (VD + 2) + VD]);
-    float l = sink ? exp2f(-m) : 0.0f;
+    float l = sink ? exp2f(sink_score - m) : 0.0f;
     for (int s = 0; s < n_splits; ++s) {
         const float ms = p[s * (VD + 2) + VD];
         if (ms != -INFINITY) l += exp2f(ms - m) * p[s * (VD + 2) + VD + 1];
@@ -570,7 +572,7 @@ Q3_EXPORT int q3_attention_capped_prefill_bf16(const void* q, const void* k_page
                                                const int* seq_start, const int* seq_pos0, const int* page_table,
                                                int pages_per_seq, int n_seqs, int max_new, int nq, int nkv, float scale,
                                                float softcap, int chunk, int sink, int window, int value_heads, int out_f32,
-                                               void* stream) {
+                                               const float* sink_values, void* stream) {
     if (n_seqs <= 0 || max_new <= 0) return 0;
     if (value_heads <= 0) value_heads = nkv;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nkv % value_heads != 0 || softcap < 0.0f || chunk < 0 || window < 0 ||
@@ -585,13 +587,13 @@ Q3_EXPORT int q3_attention_capped_prefill_bf16(const void* q, const void* k_page
         if (e != cudaSuccess) return (int)e;
         return (int)q3_launch(prefill_capped_kernel<float>, grid, dim3(WARPS * 32), PREFILL_SMEM, (cudaStream_t)stream, (const bf16*)q,
                               (const bf16*)k_pages, (const bf16*)v_pages, (float*)out, seq_start, seq_pos0, page_table,
-                              pages_per_seq, nq, nkv, scale, softcap, span, sink, value_heads);
+                              pages_per_seq, nq, nkv, scale, softcap, span, sink, value_heads, sink_values);
     }
     cudaError_t e = q3_allow_shared_memory(prefill_capped_kernel<bf16>, PREFILL_SMEM, configured[0]);
     if (e != cudaSuccess) return (int)e;
     return (int)q3_launch(prefill_capped_kernel<bf16>, grid, dim3(WARPS * 32), PREFILL_SMEM, (cudaStream_t)stream, (const bf16*)q,
                           (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, seq_start, seq_pos0, page_table,
-                          pages_per_seq, nq, nkv, scale, softcap, span, sink, value_heads);
+                          pages_per_seq, nq, nkv, scale, softcap, span, sink, value_heads, sink_values);
 }
 
 // One new token per sequence: scratch holds n_tokens * nq * n_splits * (VD + 2) float32.
@@ -599,7 +601,7 @@ Q3_EXPORT int q3_attention_capped_decode_bf16(const void* q, const void* k_pages
                                               const int* token_seq, const int* token_pos, const int* page_table,
                                               int pages_per_seq, int64_t n_tokens, int nq, int nkv, float scale, float softcap,
                                               int chunk, int sink, int n_splits, int window, int value_heads, int out_f32,
-                                              void* stream) {
+                                              const float* sink_values, void* stream) {
     if (n_tokens <= 0) return 0;
     if (value_heads <= 0) value_heads = nkv;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq / nkv > 16 || nkv % value_heads != 0 || softcap < 0.0f || chunk < 0 ||
@@ -619,9 +621,9 @@ Q3_EXPORT int q3_attention_capped_decode_bf16(const void* q, const void* k_pages
     if (e != cudaSuccess) return (int)e;
     if (out_f32)
         return (int)q3_launch(decode_capped_merge_kernel<float>, dim3(nq, (unsigned)n_tokens), dim3(VD >= 128 ? 128 : 64), 0,
-                              (cudaStream_t)stream, (const float*)scratch, (float*)out, nq, n_splits, sink);
+                              (cudaStream_t)stream, (const float*)scratch, (float*)out, nq, n_splits, sink, sink_values);
     return (int)q3_launch(decode_capped_merge_kernel<bf16>, dim3(nq, (unsigned)n_tokens), dim3(VD >= 128 ? 128 : 64), 0,
-                          (cudaStream_t)stream, (const float*)scratch, (bf16*)out, nq, n_splits, sink);
+                          (cudaStream_t)stream, (const float*)scratch, (bf16*)out, nq, n_splits, sink, sink_values);
 }
 
 // The same from the output of the q/k/v projection as it is, qkv [tokens, (nq + nkv) * D + nkv * VD]: the bias (may be null),
@@ -649,5 +651,5 @@ Q3_EXPORT int q3_attention_capped_decode_fused_bf16(const void* qkv, void* k_pag
                               scratch, token_seq, token_pos, page_table, pages_per_seq, nq, nkv, scale, softcap, chunk, fused, nkv);
     if (e != cudaSuccess) return (int)e;
     return (int)q3_launch(decode_capped_merge_kernel<bf16>, dim3(nq, (unsigned)n_tokens), dim3(VD >= 128 ? 128 : 64), 0,
-                          (cudaStream_t)stream, (const float*)scratch, (bf16*)out, nq, n_splits, sink);
+                          (cudaStream_t)stream, (const float*)scratch, (bf16*)out, nq, n_splits, sink, (const float*)nullptr);
 }

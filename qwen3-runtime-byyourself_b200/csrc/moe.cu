@@ -7,13 +7,17 @@
 //                 the `top` largest choice scores win (ties: the lower index); the weights are their plain
 //                 scores s.  The last `identity` outputs are experts without tensors whose output is the
 //                 token itself: their weights are summed into id_weight[token].
+//                 `by_logit`: the `top` largest logits win instead and the weights are the softmax over the chosen
+//                 logits only.  With `gate_out`, the router matrix has one more row after the outputs whose logit
+//                 is no expert's: gate_out[token] = sigmoid(that logit), the weight of a shared expert.
 //   moe_sort    : one block.  Counts the (token, choice) pairs of every real expert, lays the experts out one
 //                 after the other (offsets) and gives every pair its place (slot_of_pair, pair_of_slot).
 //   moe_up      : act[slot] = f(W_gate x, W_up x) for the pairs of each expert, a tile of TM pairs x 64
 //                 columns per block; g = min(gate, limit), u = clamp(up, -limit, limit),
-//                 f = g sigmoid(alpha g) (u + 1).
+//                 f = g sigmoid(alpha g) (u + up_offset)  (limit = infinity, alpha = 1, up_offset = 0: SiLU(gate) * up).
 //   moe_down    : y[slot] = W_down act[slot], the same tiling, 32-bit output.
-//   moe_combine : out[token] = T( sum_k weight_k y[slot(token, k)] + id_weight h[token] ).
+//   moe_combine : out[token] = T( sum_k weight_k y[slot(token, k)] + id_weight h[token] + shared_w[token] shared[token] ),
+//                 the last term for a shared expert that every token uses (may be absent).
 //
 // The products accumulate in 32-bit in ascending order of k whatever the tile a pair falls into, so a token's
 // result does not depend on what else is in the step.  Float tiles run on fmaf; bfloat16 tiles on the tensor cores
@@ -30,7 +34,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const T* __restrict__ h, const T* __restrict__ w_router, const float* __restrict__ correction,
                  int* __restrict__ top_ids, float* __restrict__ top_w, float* __restrict__ id_weight, int hidden, int n_out,
-                 int n_real, int top, int group_count, int group_keep) {
+                 int n_real, int top, int group_count, int group_keep, int by_logit, float* __restrict__ gate_out) {
     __shared__ float z[MAX_OUTPUTS];
     __shared__ float choice[MAX_OUTPUTS];
     __shared__ float group_best[MAX_OUTPUTS];
@@ -43,7 +47,8 @@ moe_route_kernel(const T* __restrict__ h, const T* __restrict__ w_router, const 
     // a warp per router output; 16-byte packets when the rows allow it (the order of the sum is fixed either way)
     constexpr int VEC = Pack<T>::N;
     const bool packed = hidden % VEC == 0 && aligned16_device(x) && aligned16_device(w_router);
-    for (int e = warp; e < n_out; e += 8) {
+    const int n_rows = n_out + (gate_out != nullptr ? 1 : 0);
+    for (int e = warp; e < n_rows; e += 8) {
         const T* w = w_router + (int64_t)e * hidden;
         float dot = 0.0f;
         if (packed) {
@@ -60,6 +65,32 @@ moe_route_kernel(const T* __restrict__ h, const T* __restrict__ w_router, const 
     }
     __syncthreads();
     if (tid != 0) return;
+    if (gate_out != nullptr) gate_out[t] = 1.0f / (1.0f + expf(-z[n_out]));
+    if (by_logit) {
+        // the largest logits (ties: the lower index), weighted by the softmax over the chosen logits alone
+        float best_z = 0.0f, sum = 0.0f;
+        for (int e = 0; e < n_out; ++e) choice[e] = z[e];
+        for (int k = 0; k < top; ++k) {
+            int best = -1;
+            for (int e = 0; e < n_out; ++e)
+                if (choice[e] > -INFINITY && (best < 0 || choice[e] > choice[best])) best = e;
+            if (best < 0) best = 0;
+            if (k == 0) best_z = z[best];
+            choice[best] = -INFINITY;
+            const float w = expf(z[best] - best_z);
+            top_ids[t * top + k] = best;
+            top_w[t * top + k] = w;
+            sum += w;
+        }
+        const float inv = 1.0f / sum;
+        float idw = 0.0f;
+        for (int k = 0; k < top; ++k) {
+            top_w[t * top + k] *= inv;
+            if (top_ids[t * top + k] >= n_real) idw += top_w[t * top + k];
+        }
+        id_weight[t] = idw;
+        return;
+    }
     float m = -INFINITY, sum = 0.0f;
     for (int e = 0; e < n_out; ++e) m = fmaxf(m, z[e]);
     for (int e = 0; e < n_out; ++e) {
@@ -217,7 +248,7 @@ template <typename T, int TM>
 __global__ void __launch_bounds__(256)
 moe_up_kernel(const T* __restrict__ h, const T* __restrict__ w_gate_up, const int* __restrict__ offsets,
               const int* __restrict__ pair_of_slot, T* __restrict__ act, int n_real, int top, int hidden, int ff, float limit,
-              float alpha) {
+              float alpha, float up_offset) {
     __shared__ float xs[TM * (TK + 1)], ws0[TN * (TK + 1)], ws1[TN * (TK + 1)];
     __shared__ int src_row[TM];
     pdl_launch_dependents();
@@ -239,7 +270,7 @@ moe_up_kernel(const T* __restrict__ h, const T* __restrict__ w_gate_up, const in
             const int c = col0 + tx * 4 + b;
             if (c >= ff) continue;
             const float gv = fminf(g[a][b], limit), uv = fminf(fmaxf(u[a][b], -limit), limit);
-            act[(int64_t)(row0 + rr) * ff + c] = from_f32<T>(gv / (1.0f + expf(-alpha * gv)) * (uv + 1.0f));
+            act[(int64_t)(row0 + rr) * ff + c] = from_f32<T>(gv / (1.0f + expf(-alpha * gv)) * (uv + up_offset));
         }
     }
 }
@@ -275,7 +306,7 @@ moe_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down, const i
 template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ y, const T* __restrict__ h, const int* __restrict__ slot_of_pair,
                                    const float* __restrict__ top_w, const float* __restrict__ id_weight, T* __restrict__ out,
-                                   int top, int hidden) {
+                                   int top, int hidden, const T* __restrict__ shared, const float* __restrict__ shared_w) {
     pdl_launch_dependents();
     pdl_wait();
     const int64_t t = blockIdx.x;
@@ -286,6 +317,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const T* __restr
             const int slot = slot_of_pair[t * top + k];
             if (slot >= 0) v = fmaf(top_w[t * top + k], y[(int64_t)slot * hidden + c], v);
         }
+        if (shared != nullptr) v = fmaf(shared_w[t], to_f32<T>(shared[t * hidden + c]), v);
         out[t * hidden + c] = from_f32<T>(v);
     }
 }
@@ -380,7 +412,7 @@ __device__ __forceinline__ void tile_product(const bf16* __restrict__ X, int64_t
 __global__ void __launch_bounds__(256)
 moe_up_kernel(const bf16* __restrict__ h, const bf16* __restrict__ w_gate_up, const int* __restrict__ offsets,
               const int* __restrict__ pair_of_slot, bf16* __restrict__ act, int n_real, int top, int hidden, int ff, float limit,
-              float alpha) {
+              float alpha, float up_offset) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ int src_row[BM];
     pdl_launch_dependents();
@@ -401,7 +433,7 @@ moe_up_kernel(const bf16* __restrict__ h, const bf16* __restrict__ w_gate_up, co
             const int rr = (warp & 3) * 16 + quad + (e >> 1) * 8, c = col0 + (warp >> 2) * 32 + n * 8 + tq * 2 + (e & 1);
             if (rr < rows && c < ff) {
                 const float gv = fminf(g[n][e], limit), uv = fminf(fmaxf(u[n][e], -limit), limit);
-                act[(int64_t)(row0 + rr) * ff + c] = __float2bfloat16_rn(gv / (1.0f + expf(-alpha * gv)) * (uv + 1.0f));
+                act[(int64_t)(row0 + rr) * ff + c] = __float2bfloat16_rn(gv / (1.0f + expf(-alpha * gv)) * (uv + up_offset));
             }
         }
 }
@@ -431,7 +463,7 @@ moe_down_kernel(const bf16* __restrict__ act, const bf16* __restrict__ w_down, c
 }
 
 int experts_launch(const bf16* h, const bf16* w_gate_up, const bf16* w_down, const int* offsets, const int* pair_of_slot, bf16* act,
-                   float* y, int n_pairs, int n_real, int top, int hidden, int ff, float limit, float alpha, cudaStream_t stream) {
+                   float* y, int n_pairs, int n_real, int top, int hidden, int ff, float limit, float alpha, float up_offset, cudaStream_t stream) {
     const int tiles = (n_pairs + BM - 1) / BM + n_real;          // an upper bound on the row tiles of all experts together
     if (tiles > 65535) return Q3_ERR_TOO_LARGE;
     static Q3PerDevice up_ok, down_ok;
@@ -439,7 +471,7 @@ int experts_launch(const bf16* h, const bf16* w_gate_up, const bf16* w_down, con
     if (e == cudaSuccess) e = q3_allow_shared_memory(moe_down_kernel, STAGES * 2 * TILE, down_ok);
     if (e != cudaSuccess) return (int)e;
     int code = (int)q3_launch(moe_up_kernel, dim3((ff + BN - 1) / BN, tiles), dim3(256), STAGES * 3 * TILE, stream, h, w_gate_up,
-                              offsets, pair_of_slot, act, n_real, top, hidden, ff, limit, alpha);
+                              offsets, pair_of_slot, act, n_real, top, hidden, ff, limit, alpha, up_offset);
     if (code != 0) return code;
     return (int)q3_launch(moe_down_kernel, dim3((hidden + BN - 1) / BN, tiles), dim3(256), STAGES * 2 * TILE, stream, act, w_down,
                           offsets, y, n_real, hidden, ff);
@@ -448,11 +480,11 @@ int experts_launch(const bf16* h, const bf16* w_gate_up, const bf16* w_down, con
 
 template <typename T, int TM>
 int moe_experts_launch(const T* h, const T* w_gate_up, const T* w_down, const int* offsets, const int* pair_of_slot, T* act, float* y,
-                       int n_pairs, int n_real, int top, int hidden, int ff, float limit, float alpha, cudaStream_t stream) {
+                       int n_pairs, int n_real, int top, int hidden, int ff, float limit, float alpha, float up_offset, cudaStream_t stream) {
     const int tiles = (n_pairs + TM - 1) / TM + n_real;         // an upper bound on the row tiles of all experts together
     if (tiles > 65535) return Q3_ERR_TOO_LARGE;
     int code = (int)q3_launch(moe_up_kernel<T, TM>, dim3((ff + TN - 1) / TN, tiles), dim3(256), 0, stream, h, w_gate_up, offsets,
-                              pair_of_slot, act, n_real, top, hidden, ff, limit, alpha);
+                              pair_of_slot, act, n_real, top, hidden, ff, limit, alpha, up_offset);
     if (code != 0) return code;
     return (int)q3_launch(moe_down_kernel<T, TM>, dim3((hidden + TN - 1) / TN, tiles), dim3(256), 0, stream, act, w_down, offsets, y,
                           n_real, hidden, ff);
@@ -463,34 +495,36 @@ int moe_experts_launch(const T* h, const T* w_gate_up, const T* w_down, const in
 #define Q3_MOE_EXPORTS(SUFFIX, T)                                                                                         \
     Q3_EXPORT int q3_moe_route_##SUFFIX(const void* h, const void* w_router, const float* correction, int* top_ids,       \
                                         float* top_w, float* id_weight, int64_t n_tokens, int hidden, int n_out, int n_real, \
-                                        int top, int group_count, int group_keep, void* stream) {                         \
+                                        int top, int group_count, int group_keep, int by_logit, float* gate_out,           \
+                                        void* stream) {                                                                   \
         if (n_tokens <= 0) return 0;                                                                                      \
-        if (n_out <= 0 || n_out > MAX_OUTPUTS || top <= 0 || top > n_out || n_real < 0 || n_real > n_out || \
+        if (n_out <= 0 || n_out >= MAX_OUTPUTS || top <= 0 || top > n_out || n_real < 0 || n_real > n_out || \
             group_count <= 0 || n_out % group_count != 0 || group_keep <= 0 || group_keep > group_count ||                \
             n_tokens > 0x7fffffffLL)                                                                                      \
             return Q3_ERR_BAD_SIZE;                                                                                       \
         return (int)q3_launch(moe_route_kernel<T>, dim3((unsigned)n_tokens), dim3(256), 0, (cudaStream_t)stream,          \
                               (const T*)h, (const T*)w_router, correction, top_ids, top_w, id_weight, hidden, n_out,      \
-                              n_real, top, group_count, group_keep);                                                      \
+                              n_real, top, group_count, group_keep, by_logit, gate_out);                                  \
     }                                                                                                                     \
     Q3_EXPORT int q3_moe_experts_##SUFFIX(const void* h, const void* w_gate_up, const void* w_down, const int* offsets,   \
                                           const int* pair_of_slot, void* act, float* y, int n_pairs, int n_real, int top, \
-                                          int hidden, int ff, float limit, float alpha, void* stream) {                   \
+                                          int hidden, int ff, float limit, float alpha, float up_offset, void* stream) {                   \
         if (n_pairs <= 0 || n_real <= 0) return 0;                                                                        \
         if (n_pairs <= 64)                                                                                                \
             return moe_experts_launch<T, 8>((const T*)h, (const T*)w_gate_up, (const T*)w_down, offsets, pair_of_slot,    \
-                                            (T*)act, y, n_pairs, n_real, top, hidden, ff, limit, alpha,                   \
+                                            (T*)act, y, n_pairs, n_real, top, hidden, ff, limit, alpha, up_offset,                   \
                                             (cudaStream_t)stream);                                                        \
         return moe_experts_launch<T, 32>((const T*)h, (const T*)w_gate_up, (const T*)w_down, offsets, pair_of_slot,       \
-                                         (T*)act, y, n_pairs, n_real, top, hidden, ff, limit, alpha, (cudaStream_t)stream); \
+                                         (T*)act, y, n_pairs, n_real, top, hidden, ff, limit, alpha, up_offset, (cudaStream_t)stream); \
     }                                                                                                                     \
     Q3_EXPORT int q3_moe_combine_##SUFFIX(const float* y, const void* h, const int* slot_of_pair, const float* top_w,     \
                                           const float* id_weight, void* out, int64_t n_tokens, int top, int hidden,       \
-                                          void* stream) {                                                                 \
+                                          const void* shared, const float* shared_w, void* stream) {                      \
         if (n_tokens <= 0) return 0;                                                                                      \
         if (n_tokens > 0x7fffffffLL) return Q3_ERR_BAD_SIZE;                                                              \
         return (int)q3_launch(moe_combine_kernel<T>, dim3((unsigned)n_tokens), dim3(hidden >= 1024 ? 256 : 128), 0,       \
-                              (cudaStream_t)stream, y, (const T*)h, slot_of_pair, top_w, id_weight, (T*)out, top, hidden); \
+                              (cudaStream_t)stream, y, (const T*)h, slot_of_pair, top_w, id_weight, (T*)out, top, hidden, \
+                              (const T*)shared, shared_w);                                                                \
     }
 
 Q3_EXPORT int q3_moe_sort(const int* top_ids, int n_pairs, int n_real, int* offsets, int* slot_of_pair, int* pair_of_slot,
@@ -504,12 +538,12 @@ Q3_EXPORT int q3_moe_sort(const int* top_ids, int n_pairs, int n_real, int* offs
 // bfloat16 with both widths in steps of 32 (and 16-byte aligned rows): the tensor-core tiles; else the fmaf tiles.
 Q3_EXPORT int q3_moe_experts_tc_bf16(const void* h, const void* w_gate_up, const void* w_down, const int* offsets,
                                      const int* pair_of_slot, void* act, float* y, int n_pairs, int n_real, int top, int hidden, int ff,
-                                     float limit, float alpha, void* stream) {
+                                     float limit, float alpha, float up_offset, void* stream) {
     if (n_pairs <= 0 || n_real <= 0) return 0;
     if (hidden % 32 != 0 || ff % 32 != 0 || hidden <= 0 || ff <= 0) return Q3_ERR_BAD_SIZE;
     if (!aligned16(h) || !aligned16(w_gate_up) || !aligned16(w_down) || !aligned16(act)) return Q3_ERR_MISALIGNED;
     return mma::experts_launch((const bf16*)h, (const bf16*)w_gate_up, (const bf16*)w_down, offsets, pair_of_slot, (bf16*)act, y, n_pairs,
-                               n_real, top, hidden, ff, limit, alpha, (cudaStream_t)stream);
+                               n_real, top, hidden, ff, limit, alpha, up_offset, (cudaStream_t)stream);
 }
 
 Q3_MOE_EXPORTS(f32, float)

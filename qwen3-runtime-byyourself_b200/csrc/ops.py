@@ -405,12 +405,22 @@ def qkv_prepare(qkv, q_out, k_pages, v_pages, q_norm_w, k_norm_w, cos, sin, toke
     return q_out
 
 
+def _sink_ptr(sink, sink_values, nq: int):
+    if sink_values is None:
+        return None
+    if not sink or sink_values.numel() != nq:
+        raise KernelError("attention: sink_values goes with sink and holds one float per query head")
+    return _dev(sink_values, "sink_values", torch.float32)
+
+
 def attention_generic(q, k_pages, v_pages, out, token_seq, token_pos, page_table, n_tokens: int, nq: int, nkv: int,
                       d: int, scale: float, window: Optional[int] = None, value_dim: Optional[int] = None,
-                      softcap: float = 0.0, chunk: Optional[int] = None, sink: bool = False, value_heads: Optional[int] = None):
+                      softcap: float = 0.0, chunk: Optional[int] = None, sink: bool = False, value_heads: Optional[int] = None,
+                      sink_values: Optional[torch.Tensor] = None):
     """Causal grouped-query attention of every token of the step over its sequence's pages.  `softcap` > 0 caps the
     scores smoothly (s <- softcap * tanh(s / softcap)); `chunk`: a query reads only the keys of its own chunk of that
-    many positions; `sink`: one more term exp(0), without a value, in the softmax's denominator; `value_dim`: the
+    many positions; `sink`: one more term exp(0), without a value, in the softmax's denominator (exp(sink_values[head])
+    with `sink_values`, float32 [nq]); `value_dim`: the
     size of a value head (and of an output head) if not `d`; `value_heads`: the number of value heads if not `nkv`
     (each serves nkv / value_heads key heads).  `out` has q's type, or is float32 for a caller that goes on in 32-bit."""
     s = _suffix(q)
@@ -423,12 +433,13 @@ def attention_generic(q, k_pages, v_pages, out, token_seq, token_pos, page_table
         raise KernelError("attention: a window or chunks, not both")
     fn = _fn("attention.cu", f"q3_attention_generic_{s}",
              [c_void_p] * 7 + [c_int, c_int64, c_int, c_int, c_int, c_float, c_int, c_int, c_float, c_int, c_int, c_int, c_int,
-                               c_void_p])
+                               c_void_p, c_void_p])
     _check(fn(_dev(q, "q"), _dev(k_pages, "k_pages", q.dtype), _dev(v_pages, "v_pages", q.dtype),
               _dev(out, "out"), _dev(token_seq, "token_seq", torch.int32),
               _dev(token_pos, "token_pos", torch.int32), _dev(page_table, "page_table", torch.int32),
               page_table.shape[-1], n_tokens, nq, nkv, d, float(scale), int(window or 0), vd, float(softcap or 0.0),
-              int(chunk or 0), int(bool(sink)), nv, int(out.dtype == torch.float32 and q.dtype != torch.float32), _stream()),
+              int(chunk or 0), int(bool(sink)), nv, int(out.dtype == torch.float32 and q.dtype != torch.float32),
+              _sink_ptr(sink, sink_values, nq), _stream()),
            "attention_generic")
     return out
 
@@ -550,18 +561,24 @@ def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> torch.Tensor:
 
 
 def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, top_ids: torch.Tensor, top_w: torch.Tensor,
-              id_weight: torch.Tensor, n_real: int, top: int, group_count: int = 1, group_keep: int = 1) -> None:
+              id_weight: torch.Tensor, n_real: int, top: int, group_count: int = 1, group_keep: int = 1, by_logit: bool = False,
+              gate_out: Optional[torch.Tensor] = None) -> None:
     """Router of a mixture of experts for every token of h [N, hidden]: float32 logits, softmax over all outputs,
-    choice by score + correction within the kept groups, weights = plain scores; see csrc/moe.cu."""
+    choice by score + correction within the kept groups, weights = plain scores; `by_logit`: the largest logits are
+    chosen and weighted by the softmax over the chosen logits alone (the correction is not read).  With `gate_out`
+    [N] the router matrix has one more row, and gate_out = sigmoid of its logit; see csrc/moe.cu."""
     N, hidden = h.shape
-    n_out = w_router.shape[0]
-    if w_router.shape[1] != hidden or w_router.dtype != h.dtype or correction.numel() != n_out or top_ids.numel() < N * top \
-            or top_w.numel() < N * top or id_weight.numel() < N:
+    n_out = w_router.shape[0] - (1 if gate_out is not None else 0)
+    if w_router.shape[1] != hidden or w_router.dtype != h.dtype or (correction is not None and correction.numel() != n_out) \
+            or (correction is None and not by_logit) or top_ids.numel() < N * top or top_w.numel() < N * top or id_weight.numel() < N \
+            or (gate_out is not None and gate_out.numel() < N):
         raise KernelError("moe_route: shapes do not fit")
-    fn = _fn("moe.cu", f"q3_moe_route_{_suffix(h)}", [c_void_p] * 6 + [c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
-    _check(fn(_dev(h, "h"), _dev(w_router, "w_router"), _dev(correction, "correction", torch.float32),
+    fn = _fn("moe.cu", f"q3_moe_route_{_suffix(h)}",
+             [c_void_p] * 6 + [c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(_dev(h, "h"), _dev(w_router, "w_router"), _ptr(correction, "correction", torch.float32),
               _dev(top_ids, "top_ids", torch.int32), _dev(top_w, "top_w", torch.float32), _dev(id_weight, "id_weight", torch.float32),
-              N, hidden, n_out, int(n_real), int(top), int(group_count), int(group_keep), _stream()), "moe_route")
+              N, hidden, n_out, int(n_real), int(top), int(group_count), int(group_keep), int(bool(by_logit)),
+              _ptr(gate_out, "gate_out", torch.float32), _stream()), "moe_route")
 
 
 def moe_sort(top_ids: torch.Tensor, n_pairs: int, n_real: int, offsets: torch.Tensor, slot_of_pair: torch.Tensor,
@@ -579,9 +596,10 @@ moe_tensor_cores = True      # tests switch it off to run the fmaf tiles in bflo
 
 
 def moe_experts(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, offsets: torch.Tensor, pair_of_slot: torch.Tensor,
-                act: torch.Tensor, y: torch.Tensor, n_pairs: int, n_real: int, top: int, ff: int, limit: float, alpha: float) -> None:
-    """The experts' two products for the sorted pairs: act[slot] = g sigmoid(alpha g) (u + 1) with g = min(W_gate x, limit),
-    u = clamp(W_up x, -limit, limit), then y[slot] = W_down act[slot] (float32).  w_gate_up [n_real, 2 ff, hidden] (an
+                act: torch.Tensor, y: torch.Tensor, n_pairs: int, n_real: int, top: int, ff: int, limit: float, alpha: float,
+                up_offset: float = 1.0) -> None:
+    """The experts' two products for the sorted pairs: act[slot] = g sigmoid(alpha g) (u + up_offset) with g = min(W_gate x, limit),
+    u = clamp(W_up x, -limit, limit) (limit infinity, alpha 1, up_offset 0: SiLU(gate) * up), then y[slot] = W_down act[slot] (float32).  w_gate_up [n_real, 2 ff, hidden] (an
     expert's gate rows, then its up rows), w_down [n_real, hidden, ff]."""
     hidden = h.shape[1]
     if w_gate_up.numel() != n_real * 2 * ff * hidden or w_down.numel() != n_real * hidden * ff or act.numel() < n_pairs * ff \
@@ -589,23 +607,24 @@ def moe_experts(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
         raise KernelError("moe_experts: shapes do not fit")
     tensor_cores = h.dtype == torch.bfloat16 and hidden % 32 == 0 and ff % 32 == 0 and moe_tensor_cores
     name = "q3_moe_experts_tc_bf16" if tensor_cores else f"q3_moe_experts_{_suffix(h)}"
-    fn = _fn("moe.cu", name, [c_void_p] * 7 + [c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
+    fn = _fn("moe.cu", name, [c_void_p] * 7 + [c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p])
     _check(fn(_dev(h, "h"), _dev(w_gate_up, "w_gate_up"), _dev(w_down, "w_down"), _dev(offsets, "offsets", torch.int32),
               _dev(pair_of_slot, "pair_of_slot", torch.int32), _dev(act, "act"), _dev(y, "y"), int(n_pairs), int(n_real), int(top),
-              hidden, int(ff), float(limit), float(alpha), _stream()), "moe_experts")
+              hidden, int(ff), float(limit), float(alpha), float(up_offset), _stream()), "moe_experts")
     _count_extra(1)
 
 
 def moe_combine(y: torch.Tensor, h: torch.Tensor, slot_of_pair: torch.Tensor, top_w: torch.Tensor, id_weight: torch.Tensor,
-                out: torch.Tensor, top: int) -> torch.Tensor:
-    """out[t] = sum_k top_w[t, k] y[slot_of_pair[t, k]] + id_weight[t] h[t]."""
+                out: torch.Tensor, top: int, shared: Optional[torch.Tensor] = None, shared_w: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = sum_k top_w[t, k] y[slot_of_pair[t, k]] + id_weight[t] h[t] (+ shared_w[t] shared[t])."""
     N, hidden = h.shape
-    if out.shape != h.shape or out.dtype != h.dtype:
+    if out.shape != h.shape or out.dtype != h.dtype or (shared is None) != (shared_w is None) \
+            or (shared is not None and (shared.shape != h.shape or shared.dtype != h.dtype or shared_w.numel() < N)):
         raise KernelError("moe_combine: shapes do not fit")
-    fn = _fn("moe.cu", f"q3_moe_combine_{_suffix(h)}", [c_void_p] * 6 + [c_int64, c_int, c_int, c_void_p])
+    fn = _fn("moe.cu", f"q3_moe_combine_{_suffix(h)}", [c_void_p] * 6 + [c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p])
     _check(fn(_dev(y, "y", torch.float32), _dev(h, "h"), _dev(slot_of_pair, "slot_of_pair", torch.int32),
               _dev(top_w, "top_w", torch.float32), _dev(id_weight, "id_weight", torch.float32), _dev(out, "out"), N, int(top), hidden,
-              _stream()), "moe_combine")
+              _ptr(shared, "shared"), _ptr(shared_w, "shared_w", torch.float32), _stream()), "moe_combine")
     return out
 
 
@@ -622,9 +641,10 @@ def _capped_defines(d: int, vd: int):
 
 def attention_capped_prefill(q, k_pages, v_pages, out, seq_start, seq_pos0, page_table, n_seqs: int, max_new: int, nq: int,
                              nkv: int, d: int, vd: int, scale: float, softcap: float = 0.0, chunk: Optional[int] = None,
-                             sink: bool = False, window: Optional[int] = None, value_heads: Optional[int] = None):
+                             sink: bool = False, window: Optional[int] = None, value_heads: Optional[int] = None,
+                             sink_values: Optional[torch.Tensor] = None):
     """Attention of every new token of every sequence over its pages (bfloat16, tiled, tensor cores) with capped scores,
-    chunked visibility or a sliding window, and a sink; q [tokens, nq * d], out [tokens, nq * vd] in bfloat16 or float32;
+    chunked visibility or a sliding window, and a sink (its score per query head in `sink_values`, else 0); q [tokens, nq * d], out [tokens, nq * vd] in bfloat16 or float32;
     `value_heads`: the number of value heads if not `nkv` (each serves nkv / value_heads key heads)."""
     nv = int(value_heads or nkv)
     if q.dtype != torch.bfloat16 or not attention_capped_fits(d, vd, None, 1) or out.dtype not in (torch.bfloat16, torch.float32):
@@ -632,13 +652,14 @@ def attention_capped_prefill(q, k_pages, v_pages, out, seq_start, seq_pos0, page
     if k_pages.shape[1:] != (nkv, PAGE_TOKENS, d) or v_pages.shape[1:] != (nv, PAGE_TOKENS, vd) or out.shape[-1] != nq * vd:
         raise KernelError("attention_capped_prefill: shapes do not fit")
     fn = _fn("attention_capped.cu", "q3_attention_capped_prefill_bf16",
-             [c_void_p] * 7 + [c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p],
+             [c_void_p] * 7 + [c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                               c_void_p],
              defines=_capped_defines(d, vd))
     _check(fn(_dev(q, "q"), _dev(k_pages, "k_pages", torch.bfloat16), _dev(v_pages, "v_pages", torch.bfloat16),
               _dev(out, "out"), _dev(seq_start, "seq_start", torch.int32),
               _dev(seq_pos0, "seq_pos0", torch.int32), _dev(page_table, "page_table", torch.int32), page_table.shape[-1],
               n_seqs, max_new, nq, nkv, float(scale), float(softcap or 0.0), int(chunk or 0), int(bool(sink)), int(window or 0), nv,
-              int(out.dtype == torch.float32), _stream()),
+              int(out.dtype == torch.float32), _sink_ptr(sink, sink_values, nq), _stream()),
            "attention_capped_prefill")
     return out
 
@@ -651,7 +672,8 @@ def attention_capped_splits(n_tokens: int, nkv: int, sm_count: int, max_keys: in
 
 def attention_capped_decode(q, k_pages, v_pages, out, scratch, token_seq, token_pos, page_table, n_tokens: int, nq: int,
                             nkv: int, d: int, vd: int, scale: float, softcap: float, chunk: Optional[int], sink: bool,
-                            n_splits: int, window: Optional[int] = None, value_heads: Optional[int] = None):
+                            n_splits: int, window: Optional[int] = None, value_heads: Optional[int] = None,
+                            sink_values: Optional[torch.Tensor] = None):
     """The same for one new token per sequence, the keys split over `n_splits` blocks per (token, kv head); `scratch`
     holds n_tokens * nq * n_splits * (vd + 2) float32."""
     nv = int(value_heads or nkv)
@@ -661,14 +683,15 @@ def attention_capped_decode(q, k_pages, v_pages, out, scratch, token_seq, token_
             or scratch.numel() < n_tokens * nq * n_splits * (vd + 2):
         raise KernelError("attention_capped_decode: shapes do not fit")
     fn = _fn("attention_capped.cu", "q3_attention_capped_decode_bf16",
-             [c_void_p] * 8 + [c_int, c_int64, c_int, c_int, c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+             [c_void_p] * 8 + [c_int, c_int64, c_int, c_int, c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                               c_void_p],
              defines=_capped_defines(d, vd))
     _check(fn(_dev(q, "q"), _dev(k_pages, "k_pages", torch.bfloat16), _dev(v_pages, "v_pages", torch.bfloat16),
               _dev(out, "out"), _dev(scratch, "scratch", torch.float32),
               _dev(token_seq, "token_seq", torch.int32), _dev(token_pos, "token_pos", torch.int32),
               _dev(page_table, "page_table", torch.int32), page_table.shape[-1], n_tokens, nq, nkv, float(scale),
               float(softcap or 0.0), int(chunk or 0), int(bool(sink)), int(n_splits), int(window or 0), nv,
-              int(out.dtype == torch.float32), _stream()), "attention_capped_decode")
+              int(out.dtype == torch.float32), _sink_ptr(sink, sink_values, nq), _stream()), "attention_capped_decode")
     _count_extra(1)                                              # the split kernel and the merge kernel
     return out
 
@@ -1057,4 +1080,164 @@ def attention_prefill_tc(q, k_pages, v_pages, out, seq_start, seq_pos0, page_tab
               _dev(seq_pos0, "seq_pos0", torch.int32), _dev(page_table, "page_table", torch.int32),
               page_table.shape[-1], n_seqs, max_new, n_tokens, k_pages.shape[0], nq, nkv, float(scale),
               _status_word(q.device).data_ptr(), _stream()), "attention_prefill_tc")
+    return out
+
+
+# ------------------------------------------------------------------ a float32 stream with norms of several kinds, a token shift, a side input
+NORM_KINDS = {"none": 0, "rms": 1, "dynamic_tanh": 2, "round": 3}
+
+
+def _norm_args(norm, size: int, what: str):
+    """(kind, weight, b, alpha, eps) of a norm part for `settle_norm`; None: no norm at this place.  The string
+    "round" asks for the rounded sum alone (an output only)."""
+    if norm is None:
+        return 0, None, None, 0.0, 0.0
+    if norm == "round":
+        return 3, None, None, 0.0, 0.0
+    kind = NORM_KINDS[getattr(norm, "stream_kind", "rms")]
+    w, b = norm.weight, getattr(norm, "b", None)
+    if w.numel() != size or (b is not None and b.numel() != size):
+        raise KernelError(f"settle_norm: the {what} norm's vectors do not fit the rows")
+    return kind, _dev(w, "weight", torch.float32), _ptr(b, "b", torch.float32), float(getattr(norm, "alpha", 0.0)), float(norm.eps)
+
+
+def settle_norm(stream: torch.Tensor, branch: Optional[torch.Tensor], post, pre, out: Optional[torch.Tensor],
+                rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None,
+                compute_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """One pass over the rows of the float32 `stream`: with `branch` (compute type) and the norm part `post`,
+    stream += post(branch); with `out` and `pre` (a norm part, or "round"), out = pre(stream) of the sum.  `out` is of the
+    compute type or float32.  The norm parts are RMS norms (unit rms times a weight) or dynamic-tanh norms
+    (tanh(alpha x) * weight + b).  With `rows` (int32) only those rows are read, nothing is written to the stream
+    and out[r] belongs to rows[r]."""
+    total, size = stream.shape
+    if stream.dtype != torch.float32 or (branch is None) != (post is None) or (out is None) != (pre is None):
+        raise KernelError("settle_norm: a float32 stream, a branch with its norm, an output with its norm")
+    if branch is None and out is None:
+        return None
+    dtype = branch.dtype if branch is not None else (compute_dtype or out.dtype)
+    if branch is not None and (branch.shape != stream.shape or not branch.is_contiguous()):
+        raise KernelError("settle_norm: the branch does not fit the stream")
+    n = total if rows is None else int(n_rows if n_rows is not None else rows.numel())
+    if out is not None and (out.shape[0] < n or out.shape[-1] != size or out.dtype not in (dtype, torch.float32)):
+        raise KernelError("settle_norm: the output does not fit")
+    pk, pw, pb, pa, pe = _norm_args(post, size, "post")
+    qk, qw, qb, qa, qe = _norm_args(pre, size, "pre")
+    fn = _fn("stream_shift.cu", f"q3_settle_norm_{_SUFFIX[dtype]}",
+             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_int, c_void_p, c_void_p, c_float, c_float,
+              c_void_p, c_int, c_void_p, c_int64, c_int, c_void_p])
+    _check(fn(_dev(stream, "stream"), _ptr(branch, "branch"), pk, pw, pb, pa, pe, qk, qw, qb, qa, qe, _ptr(out, "out"),
+              int(out is not None and out.dtype == torch.float32 and dtype != torch.float32),
+              _ptr(rows, "rows", torch.int32), n, size, _stream()), "settle_norm")
+    return out
+
+
+def token_shift(h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, out: torch.Tensor, token_seq: torch.Tensor,
+                seq_start: torch.Tensor, seq_slots: torch.Tensor, n_tokens: int) -> torch.Tensor:
+    """out[t] = h[t] + (h[t-1] - h[t]) * mu within every sequence (h float32, out the compute type).  The row before a
+    sequence's first row of the step is state[slot] (zero for a new sequence); the sequence's last row replaces it."""
+    size = h.shape[-1]
+    if h.dtype != torch.float32 or mu.numel() != size or state.shape[-1] != size or out.shape[-1] != size \
+            or h.shape[0] < n_tokens or out.shape[0] < n_tokens:
+        raise KernelError("token_shift: shapes do not fit")
+    fn = _fn("stream_shift.cu", f"q3_token_shift_{_suffix(out)}", [c_void_p] * 7 + [c_int64, c_int, c_void_p])
+    _check(fn(_dev(h, "h"), _dev(mu, "mu", torch.float32), _dev(state, "state", torch.float32), _dev(out, "out"),
+              _dev(token_seq, "token_seq", torch.int32), _dev(seq_start, "seq_start", torch.int32),
+              _dev(seq_slots, "seq_slots", torch.int32), int(n_tokens), size, _stream()), "token_shift")
+    return out
+
+
+def side_gate(a: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, col0: int) -> torch.Tensor:
+    """out[t, j] = gelu_tanh(a[t, j]) * table[ids[t], col0 + j]; a, out [N, dim], table [vocab, columns]."""
+    N, dim = a.shape
+    if out.shape != a.shape or out.dtype != a.dtype or table.dtype != a.dtype or ids.numel() < N:
+        raise KernelError("side_gate: shapes do not fit")
+    fn = _fn("stream_shift.cu", f"q3_side_gate_{_suffix(a)}", [c_void_p] * 4 + [c_int64, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_dev(a, "a"), _dev(ids, "ids", torch.int32), _dev(table, "table"), _dev(out, "out"), N, dim, int(col0),
+              table.shape[1], table.shape[0], _stream()), "side_gate")
+    return out
+
+
+# ------------------------------------------------------------------ linear attention whose forget gate also writes (HGRN2)
+def gated_scan(proj: torch.Tensor, state: torch.Tensor, low: torch.Tensor, bias: torch.Tensor, seq_start: torch.Tensor,
+               seq_slots: torch.Tensor, out: torch.Tensor, n_seqs: int, heads: int, d: int, vd: int) -> torch.Tensor:
+    """f = low + (1 - low) sigmoid(z + bias), S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T SiLU(q_t) over the new
+    tokens of every sequence, from and to the state rows [slot, heads, d, vd] (float32).  `proj` [N, heads (2 d + vd)]
+    holds q, z and v head by head; `out` [N, heads * vd] float32."""
+    if proj.shape[1] != heads * (2 * d + vd) or tuple(state.shape[1:]) != (heads, d, vd) or out.shape[1] != heads * vd \
+            or out.dtype != torch.float32 or low.numel() != heads * d or bias.numel() != heads * d:
+        raise KernelError("gated_scan: shapes do not fit")
+    fn = _fn("gated_recurrence.cu", f"q3_gated_scan_{_suffix(proj)}", [c_void_p] * 7 + [c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_dev(proj, "proj"), _dev(state, "state", torch.float32), _dev(low, "low", torch.float32),
+              _dev(bias, "bias", torch.float32), _dev(seq_start, "seq_start", torch.int32),
+              _dev(seq_slots, "seq_slots", torch.int32), _dev(out, "out"), int(n_seqs), heads, d, vd, _stream()), "gated_scan")
+    return out
+
+
+def head_rms_norm(o: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, vd: int) -> torch.Tensor:
+    """out = o / sqrt(mean(o^2) + eps) * weight over every run of `vd` values of a row (one weight vector for all
+    heads); o float32 [N, heads * vd], out in the compute type."""
+    if o.dtype != torch.float32 or out.shape != o.shape or weight.numel() != vd or o.shape[-1] % vd:
+        raise KernelError("head_rms_norm: shapes do not fit")
+    fn = _fn("gated_recurrence.cu", f"q3_head_rms_norm_{_suffix(out)}", [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float, c_void_p])
+    _check(fn(_dev(o, "o"), _dev(weight, "weight", torch.float32), _dev(out, "out"), o.numel() // vd, vd, float(eps), _stream()),
+           "head_rms_norm")
+    return out
+
+
+# ------------------------------------------------------------------ attention over a latent cache
+def latent_prepare(proj: torch.Tensor, kv_off: int, q_off: int, w_c: torch.Tensor, w_q: Optional[torch.Tensor],
+                   cq: Optional[torch.Tensor], k_pages: torch.Tensor, v_pages: torch.Tensor, cos, sin, token_seq, token_pos,
+                   page_table, n_tokens: int, rank: int, rot: int, rot_dims: int, interleaved: bool, eps: float,
+                   write_kv: bool = True) -> None:
+    """Per token, from the row `proj[t]`: c = unit_rms(proj[t, kv_off : kv_off + rank]) * w_c and the next `rot` values,
+    rotated by the token's position, go to the token's key row [c | rotated] in its page, c also to its value row.  With
+    `cq` [N, q_rank]: cq[t] = unit_rms(proj[t, q_off : q_off + q_rank]) * w_q, the latent of the queries."""
+    q_rank = 0 if cq is None else cq.shape[-1]
+    if proj.stride(-1) != 1 or k_pages.shape[1:] != (1, PAGE_TOKENS, rank + rot) or v_pages.shape[1:] != (1, PAGE_TOKENS, rank) \
+            or w_c.numel() != rank or (cq is not None and (w_q is None or w_q.numel() != q_rank or cq.dtype != proj.dtype)) \
+            or kv_off + rank + rot > proj.shape[1] or q_off + q_rank > proj.shape[1]:
+        raise KernelError("latent_prepare: shapes do not fit")
+    fn = _fn("latent.cu", f"q3_latent_prepare_{_suffix(proj)}",
+             [c_void_p, c_int64, c_int, c_int] + [c_void_p] * 10 + [c_int, c_int64, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                                                   c_void_p])
+    _check(fn(_dev(proj, "proj"), proj.stride(0), int(kv_off), int(q_off), _dev(w_c, "w_c", torch.float32),
+              _ptr(w_q, "w_q", torch.float32), _ptr(cq, "cq"), _dev(k_pages, "k_pages", proj.dtype),
+              _dev(v_pages, "v_pages", proj.dtype), _ptr(cos, "cos", torch.float32), _ptr(sin, "sin", torch.float32),
+              _dev(token_seq, "token_seq", torch.int32), _dev(token_pos, "token_pos", torch.int32),
+              _dev(page_table, "page_table", torch.int32), page_table.shape[-1], int(n_tokens), int(rank), int(rot), int(rot_dims),
+              int(bool(interleaved)), int(q_rank), float(eps), int(bool(write_kv)), _stream()), "latent_prepare")
+
+
+def latent_queries(q: torch.Tensor, q_full: torch.Tensor, cos, sin, token_pos, n_tokens: int, heads: int, d: int, rank: int,
+                   rot: int, rot_dims: int, interleaved: bool) -> None:
+    """q_full[t, h, rank:] = rotate(q[t, h, d:]) for q [N, heads * (d + rot)] (a view whose rows may lie apart) and
+    q_full [N, heads * (rank + rot)]."""
+    if q.shape[1] != heads * (d + rot) or q_full.shape[1] != heads * (rank + rot) or q.dtype != q_full.dtype \
+            or q.stride(-1) != 1 or not q_full.is_contiguous() or not q.is_cuda:
+        raise KernelError("latent_queries: shapes do not fit")
+    fn = _fn("latent.cu", f"q3_latent_queries_{_suffix(q)}",
+             [c_void_p, c_int64] + [c_void_p] * 4 + [c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(q.data_ptr(), q.stride(0), _dev(q_full, "q_full"), _ptr(cos, "cos", torch.float32), _ptr(sin, "sin", torch.float32),
+              _dev(token_pos, "token_pos", torch.int32), int(n_tokens), heads, d, rank, rot, int(rot_dims), int(bool(interleaved)),
+              _stream()), "latent_queries")
+
+
+def head_product(x: torch.Tensor, x_head: int, x_off: int, w: torch.Tensor, out: torch.Tensor, out_head: int, out_off: int,
+                 n_tokens: int, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t, h * out_head + out_off + j] = sum_i x[t, h * x_head + x_off + i] * w[h, i, j] for w [heads, K, N], a product per
+    head (32-bit accumulation); with `gate` (a view [N, heads * N] whose rows may lie apart) the result is multiplied by
+    sigmoid(gate[t, h * N + j])."""
+    heads, K, N = w.shape
+    if x.dtype != w.dtype or out.dtype != w.dtype or x.stride(-1) != 1 or out.stride(-1) != 1 \
+            or x_off + K > x_head or out_off + N > out_head or heads * x_head > x.shape[1] or heads * out_head > out.shape[1] \
+            or (gate is not None and (gate.dtype != w.dtype or gate.stride(-1) != 1 or gate.shape[1] != heads * N)):
+        raise KernelError("head_product: shapes do not fit")
+    fn = _fn("latent.cu", f"q3_head_product_{_suffix(w)}",
+             [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_int64, c_int64, c_int, c_int, c_int,
+              c_void_p])
+    if not (x.is_cuda and out.is_cuda and w.is_cuda and w.is_contiguous()):
+        raise KernelError("head_product: contiguous CUDA weights, CUDA operands")
+    _check(fn(x.data_ptr(), x.stride(0), int(x_head), int(x_off), w.data_ptr(), out.data_ptr(), out.stride(0), int(out_head),
+              int(out_off), None if gate is None else gate.data_ptr(), 0 if gate is None else gate.stride(0), int(n_tokens), heads, K, N,
+              _stream()), "head_product")
     return out

@@ -23,4 +23,7 @@ def all_variants():
         ("differential.cu", ()),
         ("moe.cu", ()),
         ("attention_capped.cu", ("Q3_HEAD_DIM=64", "Q3_VALUE_DIM=128")),
+        ("stream_shift.cu", ()),
+        ("gated_recurrence.cu", ()),
+        ("latent.cu", ()),
     ]

@@ -92,15 +92,16 @@ int q3_qkv_prepare_bf16(const void* qkv, void* q_out, void* k_pages, void* v_pag
    causal grouped-query attention of every token over its sequence's pages; window 0 = every key; value_dim 0 = d;
    value_heads 0 = nkv, else each value head serves nkv / value_heads key heads; out_f32: `out` is float whatever q is;
    softcap > 0: scores s <- softcap * tanh(s / softcap); chunk > 0: a query reads the keys of its own chunk of that many
-   positions only; sink != 0: one more term exp(0) in the softmax's denominator */
+   positions only; sink != 0: one more term exp(0) in the softmax's denominator, or exp(sink_values[head]) where sink_values
+   (one float per query head) is given */
 int q3_attention_generic_f32(const void* q, const void* k_pages, const void* v_pages, void* out, const int* token_seq,
                              const int* token_pos, const int* page_table, int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d,
                              float scale, int window, int value_dim, float softcap, int chunk, int sink, int value_heads, int out_f32,
-                             void* stream);
+                             const float* sink_values, void* stream);
 int q3_attention_generic_bf16(const void* q, const void* k_pages, const void* v_pages, void* out, const int* token_seq,
                               const int* token_pos, const int* page_table, int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d,
                               float scale, int window, int value_dim, float softcap, int chunk, int sink, int value_heads, int out_f32,
-                             void* stream);
+                              const float* sink_values, void* stream);
 
 /* the same from the q/k/v projection's output as it is: bias (may be null), rotation of the first rotary_dim values of q and k
    (tables may be null) and the write of the new key and value into their pages in the attention's own kernel */
@@ -122,14 +123,14 @@ int q3_attention_capped_value_dim(void);
 int q3_attention_capped_prefill_bf16(const void* q, const void* k_pages, const void* v_pages, void* out, const int* seq_start,
                                      const int* seq_pos0, const int* page_table, int pages_per_seq, int n_seqs, int max_new, int nq,
                                      int nkv, float scale, float softcap, int chunk, int sink, int window, int value_heads,
-                                     int out_f32, void* stream);
+                                     int out_f32, const float* sink_values, void* stream);
 /* (window > 0: a sliding window of that many keys instead of chunks; value_heads 0 = nkv, else each value head serves
-   nkv / value_heads key heads; out_f32: `out` is float) */
+   nkv / value_heads key heads; out_f32: `out` is float; sink_values (may be null): the sink's score per query head) */
 /* one new token per sequence; scratch: n_tokens * nq * n_splits * (value_dim + 2) float32 */
 int q3_attention_capped_decode_bf16(const void* q, const void* k_pages, const void* v_pages, void* out, float* scratch,
                                     const int* token_seq, const int* token_pos, const int* page_table, int pages_per_seq,
                                     int64_t n_tokens, int nq, int nkv, float scale, float softcap, int chunk, int sink, int n_splits,
-                                    int window, int value_heads, int out_f32, void* stream);
+                                    int window, int value_heads, int out_f32, const float* sink_values, void* stream);
 
 /* ---- attention_decode.cu (-DQ3_HEAD_DIM): one new token per sequence, bfloat16 ---------------------------- */
 int q3_attention_decode_head_dim(void);
@@ -233,29 +234,88 @@ int q3_diff_combine_bf16(const float* a, void* out, int64_t n_tokens, int heads,
 
 /* ---- moe.cu: a routed feed-forward ---------------------------------------------------------------------------- */
 /* per token: float32 router logits, softmax, choice by score + correction within the kept groups, weights = scores;
-   the outputs from n_real on are identity experts (their weights are summed into id_weight) */
+   the outputs from n_real on are identity experts (their weights are summed into id_weight); by_logit: the largest logits
+   are chosen, weighted by the softmax over the chosen logits alone; gate_out (may be null): the router matrix has one more
+   row and gate_out[t] = sigmoid of its logit */
 int q3_moe_route_f32(const void* h, const void* w_router, const float* correction, int* top_ids, float* top_w, float* id_weight,
-                     int64_t n_tokens, int hidden, int n_out, int n_real, int top, int group_count, int group_keep, void* stream);
+                     int64_t n_tokens, int hidden, int n_out, int n_real, int top, int group_count, int group_keep, int by_logit,
+                      float* gate_out, void* stream);
 int q3_moe_route_bf16(const void* h, const void* w_router, const float* correction, int* top_ids, float* top_w, float* id_weight,
-                      int64_t n_tokens, int hidden, int n_out, int n_real, int top, int group_count, int group_keep, void* stream);
+                      int64_t n_tokens, int hidden, int n_out, int n_real, int top, int group_count, int group_keep, int by_logit,
+                      float* gate_out, void* stream);
 /* offsets [n_real + 1], slot_of_pair (-1: identity) and pair_of_slot of the (token, choice) pairs laid out by expert */
 int q3_moe_sort(const int* top_ids, int n_pairs, int n_real, int* offsets, int* slot_of_pair, int* pair_of_slot, void* stream);
-/* act[slot] = g sigmoid(alpha g) (u + 1), g = min(W_gate x, limit), u = clamp(W_up x, -limit, limit); y[slot] = W_down act */
+/* act[slot] = g sigmoid(alpha g) (u + up_offset), g = min(W_gate x, limit), u = clamp(W_up x, -limit, limit); y[slot] = W_down act */
 int q3_moe_experts_f32(const void* h, const void* w_gate_up, const void* w_down, const int* offsets, const int* pair_of_slot,
                        void* act, float* y, int n_pairs, int n_real, int top, int hidden, int ff, float limit, float alpha,
-                       void* stream);
+                       float up_offset, void* stream);
 int q3_moe_experts_bf16(const void* h, const void* w_gate_up, const void* w_down, const int* offsets, const int* pair_of_slot,
                         void* act, float* y, int n_pairs, int n_real, int top, int hidden, int ff, float limit, float alpha,
-                        void* stream);
+                        float up_offset, void* stream);
 /* the same on the tensor cores: bfloat16, hidden and ff multiples of 32 */
 int q3_moe_experts_tc_bf16(const void* h, const void* w_gate_up, const void* w_down, const int* offsets, const int* pair_of_slot,
                            void* act, float* y, int n_pairs, int n_real, int top, int hidden, int ff, float limit, float alpha,
-                           void* stream);
-/* out[t] = sum_k top_w[t, k] y[slot_of_pair[t, k]] + id_weight[t] h[t] */
+                           float up_offset, void* stream);
+/* out[t] = sum_k top_w[t, k] y[slot_of_pair[t, k]] + id_weight[t] h[t] + shared_w[t] shared[t] (the last may be null) */
 int q3_moe_combine_f32(const float* y, const void* h, const int* slot_of_pair, const float* top_w, const float* id_weight,
-                       void* out, int64_t n_tokens, int top, int hidden, void* stream);
+                       void* out, int64_t n_tokens, int top, int hidden, const void* shared, const float* shared_w, void* stream);
 int q3_moe_combine_bf16(const float* y, const void* h, const int* slot_of_pair, const float* top_w, const float* id_weight,
-                        void* out, int64_t n_tokens, int top, int hidden, void* stream);
+                        void* out, int64_t n_tokens, int top, int hidden, const void* shared, const float* shared_w, void* stream);
+
+/* ---- stream_shift.cu: a float32 hidden state with norms of several kinds, a token shift, a token side input ------ */
+/* one pass over the rows: stream += post(branch), out = pre(stream).  Norm kinds: 0 none, 1 unit rms times w, 2 dynamic tanh
+   tanh(alpha x) * w + b, 3 the rounded sum alone (pre only).  out_f32: `out` is float whatever the compute type.  With `rows`
+   only those rows are read, nothing is written to the stream and out[r] belongs to rows[r] */
+int q3_settle_norm_f32(float* stream_rows, const void* branch, int post_kind, const float* post_w, const float* post_b,
+                       float post_alpha, float post_eps, int pre_kind, const float* pre_w, const float* pre_b, float pre_alpha,
+                       float pre_eps, void* out, int out_f32, const int* rows, int64_t n_rows, int size, void* stream);
+int q3_settle_norm_bf16(float* stream_rows, const void* branch, int post_kind, const float* post_w, const float* post_b,
+                        float post_alpha, float post_eps, int pre_kind, const float* pre_w, const float* pre_b, float pre_alpha,
+                        float pre_eps, void* out, int out_f32, const int* rows, int64_t n_rows, int size, void* stream);
+/* out[t] = h[t] + (h[t-1] - h[t]) * mu within a sequence; the row before a step's first row is state[slot], which the step's
+   last row replaces */
+int q3_token_shift_f32(const float* h, const float* mu, float* state, void* out, const int* token_seq, const int* seq_start,
+                       const int* seq_slots, int64_t n_tokens, int size, void* stream);
+int q3_token_shift_bf16(const float* h, const float* mu, float* state, void* out, const int* token_seq, const int* seq_start,
+                        const int* seq_slots, int64_t n_tokens, int size, void* stream);
+/* out[t, j] = gelu_tanh(a[t, j]) * table[ids[t], col0 + j] */
+int q3_side_gate_f32(const void* a, const int* ids, const void* table, void* out, int64_t n_tokens, int dim, int col0,
+                     int table_cols, int vocab, void* stream);
+int q3_side_gate_bf16(const void* a, const int* ids, const void* table, void* out, int64_t n_tokens, int dim, int col0,
+                      int table_cols, int vocab, void* stream);
+
+/* ---- gated_recurrence.cu: linear attention whose forget gate also writes, a float32 state [slot, heads, d, vd] --------- */
+/* proj [tokens, heads (2 d + vd)]: q, gate logits and v head by head; f = low + (1 - low) sigmoid(z + bias),
+   S = diag(f) S + (1 - f) v^T, out = S^T silu(q) (float32 [tokens, heads vd]) */
+int q3_gated_scan_f32(const void* proj, float* state, const float* low, const float* bias, const int* seq_start,
+                      const int* seq_slots, float* out, int n_seqs, int heads, int d, int vd, void* stream);
+int q3_gated_scan_bf16(const void* proj, float* state, const float* low, const float* bias, const int* seq_start,
+                       const int* seq_slots, float* out, int n_seqs, int heads, int d, int vd, void* stream);
+/* out = o / sqrt(mean(o^2) + eps) * w over every run of vd values (n_rows runs) */
+int q3_head_rms_norm_f32(const float* o, const float* w, void* out, int64_t n_rows, int vd, float eps, void* stream);
+int q3_head_rms_norm_bf16(const float* o, const float* w, void* out, int64_t n_rows, int vd, float eps, void* stream);
+
+/* ---- latent.cu: attention over a cache of latents [c | rotated key part] ---------------------------------------------- */
+/* per token: c = unit_rms(proj[kv_off : kv_off + rank]) * w_c and the next `rot` values rotated go to the key row, c also to the
+   value row; with q_rank > 0, cq = unit_rms(proj[q_off : q_off + q_rank]) * w_q */
+int q3_latent_prepare_f32(const void* proj, int64_t proj_stride, int kv_off, int q_off, const float* w_c, const float* w_q, void* cq,
+                          void* k_pages, void* v_pages, const float* cos_tab, const float* sin_tab, const int* token_seq,
+                          const int* token_pos, const int* page_table, int pages_per_seq, int64_t n_tokens, int rank, int rot,
+                          int rot_dims, int interleaved, int q_rank, float eps, int write_kv, void* stream);
+int q3_latent_prepare_bf16(const void* proj, int64_t proj_stride, int kv_off, int q_off, const float* w_c, const float* w_q, void* cq,
+                           void* k_pages, void* v_pages, const float* cos_tab, const float* sin_tab, const int* token_seq,
+                           const int* token_pos, const int* page_table, int pages_per_seq, int64_t n_tokens, int rank, int rot,
+                           int rot_dims, int interleaved, int q_rank, float eps, int write_kv, void* stream);
+/* q_full[t, h, rank:] = rotate(q[t, h, d:]) */
+int q3_latent_queries_f32(const void* q, int64_t q_row, void* q_full, const float* cos_tab, const float* sin_tab, const int* token_pos,
+                          int64_t n_tokens, int heads, int d, int rank, int rot, int rot_dims, int interleaved, void* stream);
+int q3_latent_queries_bf16(const void* q, int64_t q_row, void* q_full, const float* cos_tab, const float* sin_tab, const int* token_pos,
+                           int64_t n_tokens, int heads, int d, int rank, int rot, int rot_dims, int interleaved, void* stream);
+/* out[t, h, out_off + j] = sum_i x[t, h, x_off + i] * w[h, i, j] (* sigmoid(gate[t, h, j]) where gate is given) */
+int q3_head_product_f32(const void* x, int64_t x_row, int x_head, int x_off, const void* w, void* out, int64_t out_row, int out_head,
+                        int out_off, const void* gate, int64_t gate_row, int64_t n_tokens, int heads, int K, int N, void* stream);
+int q3_head_product_bf16(const void* x, int64_t x_row, int x_head, int x_off, const void* w, void* out, int64_t out_row, int out_head,
+                         int out_off, const void* gate, int64_t gate_row, int64_t n_tokens, int heads, int K, int N, void* stream);
 
 /* ---- sampling.cu ------------------------------------------------------------------------------------------ */
 /* out[r] = index of the highest logit among the first `valid` (lowest id among equals, NaN as -inf) */

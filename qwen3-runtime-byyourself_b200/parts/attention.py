@@ -52,6 +52,7 @@ class GQAAttention(Part):
                  window: Optional[int] = None, prefix: str = "", value_dim: Optional[int] = None, bias: bool = False,
                  softcap: Optional[float] = None, chunk: Optional[int] = None, sink: bool = False,
                  names: Optional[dict] = None, value_heads: Optional[int] = None, out_float32: bool = False):
+        self.sink_values = None      # float32 [num_heads]: the sink's score per head, for a part that has learned ones (else 0)
         if num_heads % num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         value_dim = int(value_dim or head_dim)
@@ -184,7 +185,7 @@ class GQAAttention(Part):
         ops.attention_generic(q, cache.keys, cache.values, out, ctx.token_seq, ctx.token_pos, table, ctx.n_tokens,
                               self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.window,
                               value_dim=self.value_dim, softcap=self.softcap, chunk=self.chunk, sink=self.sink,
-                              value_heads=self.value_heads)
+                              value_heads=self.value_heads, sink_values=self.sink_values)
 
     def _prepare_unfused(self, qkv, q, cache, ctx, table, qw, kw, eps) -> None:
         """A position encoding without kernel tables: norm, then `apply_`, then the cache write."""
@@ -303,7 +304,8 @@ def _prefill_capped_kernel(part, q, cache, out, ctx, table) -> bool:
         return False
     ops.attention_capped_prefill(q, cache.keys, cache.values, out, ctx.seq_start, ctx.seq_pos0, table, ctx.n_seqs, ctx.max_new,
                                  part.num_heads, part.num_kv_heads, part.head_dim, part.value_dim, part.scale, part.softcap,
-                                 part.chunk, part.sink, window=part.window, value_heads=part.value_heads)
+                                 part.chunk, part.sink, window=part.window, value_heads=part.value_heads,
+                                 sink_values=part.sink_values)
     return True
 
 
@@ -311,7 +313,7 @@ def _prefill_capped_tcgen05_kernel(part, q, cache, out, ctx, table) -> bool:
     """The same on tcgen05 with TMA-fed tiles: head sizes 64 and 128, values as wide as keys, and enough new tokens
     for 128-row tiles to be worth it."""
     if part.plain or part.shared_values or not ops.attention_capped_prefill_tc_fits(part.head_dim, part.value_dim, part.window) \
-            or ctx.max_new < tc_prefill_rows or part.scale <= 0:
+            or ctx.max_new < tc_prefill_rows or part.scale <= 0 or part.sink_values is not None:
         return False
     ops.attention_capped_prefill_tc(q[:ctx.n_tokens], cache.keys, cache.values, out, ctx.seq_start, ctx.seq_pos0, table,
                                     ctx.n_seqs, ctx.max_new, ctx.n_tokens, part.num_heads, part.num_kv_heads, part.head_dim,
@@ -329,14 +331,14 @@ def _decode_capped_kernel(part, q, cache, out, ctx, table) -> bool:
     scratch = ctx.scratch.get("attn.capped_scratch", (ctx.n_tokens * nq * splits * (part.value_dim + 2),), torch.float32)
     ops.attention_capped_decode(q, cache.keys, cache.values, out, scratch, ctx.token_seq, ctx.token_pos, table, ctx.n_tokens,
                                 nq, nkv, part.head_dim, part.value_dim, part.scale, part.softcap, part.chunk, part.sink, splits,
-                                window=part.window, value_heads=part.value_heads)
+                                window=part.window, value_heads=part.value_heads, sink_values=part.sink_values)
     return True
 
 
 def _decode_capped_fused_kernel(part, qkv, cache, out, ctx, table, q_norm_w, k_norm_w, eps, cos, sin) -> bool:
     """Bias, rotation, cache write and the split-key attention of a decode step in one kernel (and the small merge)."""
     nq, nkv = part.num_heads, part.num_kv_heads
-    if part.plain or part.shared_values or part.window or q_norm_w is not None or cache.shared \
+    if part.plain or part.shared_values or part.window or q_norm_w is not None or cache.shared or part.sink_values is not None \
             or not ops.attention_capped_fits(part.head_dim, part.value_dim, part.window, nq // nkv):
         return False
     splits = ops.attention_capped_splits(ctx.n_tokens, nkv, _sm_count(ctx.device), part.chunk or ctx.max_context)

@@ -100,6 +100,118 @@ class SandwichNormBlock(Part):
         return residual, NormedBranch(self.feed_forward.forward(normed, ctx), self.norms[3])
 
 
+class ShiftSandwichBlock(Part):
+    """Sandwich-norm sublayers on a float32 stream, x += norm_b(mixer(shift(norm_a(x)))), then the same around the
+    feed-forward without the shift (a layer may lack it), with norms of any kind that `ops.settle_norm` takes.
+
+    Token shift: what the mixer reads, h, becomes h_t + (h_(t-1) - h_t) * mu with mu the vector `shift_name`, h_(t-1) the
+    row before it in the sequence as it was before this step (zeros before the first token).  The last h of a sequence
+    is part of its state: `state_size` float32 values per sequence in the layer's cache (`LayerCache.block_state`).
+
+    Token side input (`side`, optional), after the feed-forward: with e the columns [index * dim, (index + 1) * dim) of
+    a second embedding table that all layers share, g = gelu_tanh(W_gate x) * e, y = W_proj g and
+    x += y / sqrt(mean(y^2) + eps) * w.  `side` = {table, vocab, columns, dim, index, eps, gate, proj, norm}, the names
+    relative to the layer's prefix but for `table`.
+
+    Every sum is left pending and done by the next reader's kernel, which normalises the sum for its own input."""
+    stream_dtype = "float32"
+
+    def __init__(self, mixer, feed_forward, norm: PartSpec, hidden_size: int, names=("norm1", "norm1b", "norm2", "norm2b"),
+                 shift_name: str = "shift", side=None):
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.hidden_size, self.names, self.shift_name = int(hidden_size), tuple(names), shift_name
+        self.norms = [build_part("norm", norm) for _ in range(4 if feed_forward is not None else 2)]
+        self.state_size = self.hidden_size
+        self.mu = None
+        self.side = dict(side) if side else None
+        self.side_norm = self.side_table = self.w_side_gate = self.w_side_proj = None
+        if self.side:
+            self.side_norm = build_part("norm", PartSpec("rms_norm", {"size": self.hidden_size, "eps": self.side["eps"]}))
+
+    def weight_specs(self, prefix: str) -> dict:
+        from ..weights.loader import WeightSpec
+        specs, H = {}, self.hidden_size
+        for part, name in zip(self.norms, self.names):
+            specs.update(part.weight_specs(prefix + name))
+        specs[prefix + self.shift_name] = WeightSpec((H,), "bias")
+        if self.side:
+            sd = self.side
+            specs[sd["table"]] = WeightSpec((sd["vocab"], sd["columns"]))
+            specs[prefix + sd["gate"]] = WeightSpec((sd["dim"], H))
+            specs[prefix + sd["proj"]] = WeightSpec((H, sd["dim"]))
+            specs.update(self.side_norm.weight_specs(prefix + sd["norm"]))
+        specs.update(self.mixer.weight_specs(prefix))
+        if self.feed_forward is not None:
+            specs.update(self.feed_forward.weight_specs(prefix))
+        return specs
+
+    def ignorable(self, prefix: str):
+        """The norms of a feed-forward that the layer does not have may be stored all the same."""
+        if self.feed_forward is not None:
+            return []
+        return [n for name in self.names[2:] for n in self.norms[0].weight_specs(prefix + name)]
+
+    def bind(self, weights: dict, prefix: str, dtype, device) -> None:
+        import torch
+        for part, name in zip(self.norms, self.names):
+            part.bind(weights, prefix + name, dtype, device)
+        self.mu = weights[prefix + self.shift_name].to(device=device, dtype=torch.float32).contiguous()
+        if self.side:
+            sd = self.side
+            self.side_table = weights[sd["table"]]           # one tensor for all layers: not taken out of `weights`
+            self.w_side_gate = weights.pop(prefix + sd["gate"]).contiguous()
+            self.w_side_proj = weights.pop(prefix + sd["proj"]).contiguous()
+            self.side_norm.bind(weights, prefix + sd["norm"], dtype, device)
+        self.mixer.bind(weights, prefix, dtype, device)
+        if self.feed_forward is not None:
+            self.feed_forward.bind(weights, prefix, dtype, device)
+
+    @staticmethod
+    def _settle(residual, pending, norm, out):
+        from ..csrc import ops
+        if pending is not None and not isinstance(pending, NormedBranch):
+            raise TypeError("a float32 stream takes a NormedBranch as its pending sum")
+        return ops.settle_norm(residual, pending.branch if pending else None, pending.norm if pending else None, norm, out)
+
+    def forward(self, residual, delta, ctx, cache):
+        import torch
+        from ..csrc import ops
+        from .linear import linear
+        N, H = ctx.n_tokens, self.hidden_size
+        if cache.block_state is None:
+            raise ops.KernelError("the token shift keeps a row per sequence: the cache was built without block_state")
+        h = ctx.scratch.get("block.h32", (N, H), torch.float32)
+        self._settle(residual, delta, self.norms[0], h)
+        shifted = ctx.scratch.get("block.normed", (N, H), ctx.dtype)
+        ops.token_shift(h, self.mu, cache.block_state, shifted, ctx.token_seq, ctx.seq_start, ctx.seq_slots, N)
+        pending = NormedBranch(self.mixer.forward(shifted, ctx, cache), self.norms[1])
+        if self.feed_forward is not None:
+            normed = ctx.scratch.get("block.normed", (N, H), ctx.dtype)
+            self._settle(residual, pending, self.norms[2], normed)
+            pending = NormedBranch(self.feed_forward.forward(normed, ctx), self.norms[3])
+        if self.side:
+            sd = self.side
+            rounded = ctx.scratch.get("block.normed", (N, H), ctx.dtype)
+            self._settle(residual, pending, "round", rounded)
+            a = ctx.scratch.get("side.a", (N, sd["dim"]), ctx.dtype)
+            linear(rounded, self.w_side_gate, a)
+            g = ctx.scratch.get("side.g", (N, sd["dim"]), ctx.dtype)
+            ops.side_gate(a, ctx.token_ids, self.side_table, g, sd["index"] * sd["dim"])
+            y = ctx.scratch.get("side.out", (N, H), ctx.dtype)
+            pending = NormedBranch(linear(g, self.w_side_proj, y), self.side_norm)
+        return residual, pending
+
+    def finish(self, residual, pending, final_norm, ctx, out, normalize: bool = True):
+        """out[r] = final_norm(stream + pending) of wanted row r (the pending sum is done in registers for those rows
+        only: nothing reads the stream after the tail)."""
+        from ..csrc import ops
+        if ctx.want_all:
+            return self._settle(residual, pending, final_norm if normalize else "round", out)
+        return ops.settle_norm(residual, pending.branch if pending else None, pending.norm if pending else None,
+                               final_norm if normalize else "round", out, rows=ctx.want_rows[:ctx.n_want], n_rows=ctx.n_want,
+                               compute_dtype=ctx.dtype)
+
+
 class HyperPending:
     """A sublayer's output (compute type) that is still to be added to the streams: every stream becomes a mix of the
     old streams plus its share of the output."""
@@ -202,3 +314,4 @@ class HyperConnectionBlock(Part):
 register_part("block", "hyper_connections", HyperConnectionBlock)
 register_part("block", "pre_norm", PreNormBlock)
 register_part("block", "sandwich_norm", SandwichNormBlock)
+register_part("block", "shift_sandwich", ShiftSandwichBlock)

@@ -9,6 +9,7 @@ last).
 """
 from __future__ import annotations
 
+import dataclasses
 import sys
 from typing import Dict, List, Optional
 
@@ -95,7 +96,9 @@ class Model:
             if owner is None or self.plan.layers[owner].cache_from is not None:
                 needs.append(None)
             else:
-                needs.append(self.blocks[owner].mixer.cache_need())
+                need = self.blocks[owner].mixer.cache_need()
+                extra = int(getattr(self.blocks[owner], "state_size", 0) or 0)     # what the block itself keeps per sequence
+                needs.append(dataclasses.replace(need, block_state=extra) if extra else need)
         return needs
 
     def cache_sources(self) -> Dict[int, int]:

@@ -27,16 +27,17 @@ class RotaryEmbedding(Part):
     fused_tables = True   # exposes cos/sin [positions, rotary_dim/2] float32 for a kernel to read
 
     def __init__(self, head_dim: int, theta: float, max_positions: int, rotary_dim: int = 0, interleaved: bool = False,
-                 scaling: Optional[dict] = None):
+                 scaling: Optional[dict] = None, theta_float32: bool = True):
         """`rotary_dim` (default: the head size, as in Qwen3): only the first `rotary_dim` values of a head are
         rotated, in pairs (i, i + rotary_dim/2) with inv_freq_i = theta^(-2i/rotary_dim); the rest pass through.
-        `interleaved`: pairs (2i, 2i + 1) instead.  `scaling`: {factor, low, high, original}, see the top of the file."""
+        `interleaved`: pairs (2i, 2i + 1) instead.  `scaling`: {factor, low, high, original}, see the top of the file.
+        `theta_float32`: theta is rounded to a 32-bit float first, as the reference holds it; False takes it as given."""
         rotary_dim = int(rotary_dim) or int(head_dim)
         if rotary_dim % 2 or not 0 < rotary_dim <= head_dim:
             raise ValueError("rotary encoding needs an even rotary_dim within the head")
         self.head_dim, self.theta, self.max_positions = int(head_dim), float(theta), int(max_positions)
         self.rotary_dim = rotary_dim
-        self.interleaved = bool(interleaved)
+        self.interleaved, self.theta_float32 = bool(interleaved), bool(theta_float32)
         self.scaling = None
         if scaling:
             self.scaling = {k: float(scaling[k]) for k in ("factor", "low", "high", "original")}
@@ -48,7 +49,7 @@ class RotaryEmbedding(Part):
         """The rotary_dim / 2 angular frequencies, in float64, after the rescaling by wavelength."""
         half = self.rotary_dim // 2
         # theta is held as a 32-bit float by the reference (include/qwen3/model/config.h:22)
-        theta = float(torch.tensor(self.theta, dtype=torch.float32).item())
+        theta = float(torch.tensor(self.theta, dtype=torch.float32).item()) if self.theta_float32 else self.theta
         freq = [math.pow(theta, -(2.0 * i) / self.rotary_dim) for i in range(half)]
         if self.scaling:
             sc = self.scaling

@@ -123,7 +123,7 @@ def save_file(tensors: Dict[str, torch.Tensor], path: str, metadata: Optional[Di
         f.write(raw)
         for t in tensors.values():
             c = t.detach().to("cpu").contiguous()
-            f.write(c.view(torch.uint8).numpy().tobytes() if c.numel() else b"")
+            f.write(c.reshape(-1).view(torch.uint8).numpy().tobytes() if c.numel() else b"")
     return offset
 
 

@@ -174,7 +174,7 @@ class CheckpointUpload:
         rows = 1
         for s in info.shape[:-1]:
             rows *= s
-        if not info.shape or rows * cols == 0:
+        if rows * cols == 0:                                            # (a tensor without axes is one row of one value)
             return
         item = torch.empty((), dtype=info.dtype).element_size()
         row_bytes = cols * item
