@@ -4,6 +4,7 @@ model with random weights in bfloat16 on one B200, batch 8 at a context of 4,096
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--shape 8b|14b|32b]
     python bench.py --designs        (another measurement: a Dozazen model beside Qwen3 at equal sizes)
     python bench.py --designs lagulorn   (the same for a Lagulorn model)
+    python bench.py --designs fagunex    (a Fagunex model beside the Lagulorn model of the same widths)
 
 Prints ONE JSON line.  A "step" is one decode step of the whole batch.
   value     decoded tokens a second, timed on the device with CUDA events around K steps;
@@ -447,6 +448,39 @@ def lagulorn_side_by_side(q, torch, Sampler, steps, warmup, batch=8, context=409
     return out
 
 
+def fagunex_config(width, heads, d, ff, layers, window=1024, experts=16, top=2):
+    """A Fagunex model of the widths of the Lagulorn model beside it: latent attention with a window, with queries through
+    a latent, a sink and an output gate; the gated recurrence (heads of d x d); latent attention over every earlier key;
+    the recurrence again; and so on.  A cache row is a latent of 4 d values and d / 2 rotated ones for all heads together.
+    Every layer's feed-forward is routed (`experts` experts of ff / (2 top), `top` per token) with a shared expert of the same
+    size beside them; a token side input of 64 values per layer."""
+    rot = {"base": 1000000.0, "dims": d // 2}
+    latent = {"heads": heads, "dim": d, "rot_dim": d // 2, "vdim": d, "kv_rank": 4 * d, "scale": (d + d // 2) ** -0.5, "rot": rot}
+    first = {"type": "latent_attention", "mixer": dict(latent, q_rank=width * 3 // 4, mask={"size": window})}
+    second = {"type": "latent_attention_2", "mixer": dict(latent)}
+    recurrent = {"type": "hgrn2", "mixer": {"heads": heads, "dim": d, "vdim": d}}
+    moe = {"kind": "moe", "expert": {"ff": ff // (2 * top)}, "router": {"experts": experts, "top": top}, "shared": {"ff": ff // (2 * top)}}
+    order = [first, recurrent, second, recurrent]
+    return {"architecture": "Fagunex", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-6}, "token_side": {"dim": 64},
+            "layers": [dict(order[i % 4], mlp=moe) for i in range(layers)]}
+
+
+def fagunex_side_by_side(q, torch, Sampler, steps, warmup, batch=8, context=4096):
+    """Fagunex beside Lagulorn, the closest of the other designs (a 32-bit hidden state, attention with a window in turn with
+    a recurrence, routed experts), at equal widths (random weights, bfloat16): decode at `batch` x `context`, a prompt step of
+    2,048 tokens, and the time of every kernel of one step of each kind."""
+    import numpy as np
+    out = {"batch": batch, "context": context, "prompt_tokens": PREFILL_TOKENS, "vocab": DESIGN_VOCAB, "sizes": {}}
+    for name, width, heads, kv, d, ff, layers in DESIGN_SIZES:
+        row = {"width": width, "heads": heads, "kv_heads": kv, "head_dim": d, "ff": ff, "layers": layers}
+        row["fagunex"] = design_point(q, torch, Sampler, fagunex_config(width, heads, d, ff, layers), np.random.default_rng(0),
+                                      batch, context, steps, warmup)
+        row["lagulorn"] = design_point(q, torch, Sampler, lagulorn_config(width, heads, kv, d, ff, layers), np.random.default_rng(0),
+                                       batch, context, steps, warmup)
+        out["sizes"][name] = row
+    return out
+
+
 def designs_side_by_side(q, torch, Sampler, steps, warmup, batch=8, context=4096):
     """Dozazen beside Qwen3 at equal sizes (random weights, bfloat16): decode at `batch` x `context`, a prompt step of
     2,048 tokens; chunks longer than the context (every key is read, as in Qwen3) and chunks of 1,024."""
@@ -482,9 +516,10 @@ def main() -> int:
     ap.add_argument("--kernels", action="store_true",
                     help="instead of the benchmark: time every kernel of one decode step and of one 2,048-token prompt step "
                          "with CUDA events (steps launched afresh, not replayed) and print the sums per entry point")
-    ap.add_argument("--designs", nargs="?", const="dozazen", default=None, choices=["dozazen", "lagulorn"],
+    ap.add_argument("--designs", nargs="?", const="dozazen", default=None, choices=["dozazen", "lagulorn", "fagunex"],
                     help="instead of the benchmark: decode and prompt throughput of a Dozazen (default) or Lagulorn model beside "
-                         "the Qwen3 model of the same widths at two sizes, with the time of every kernel of one step of each kind")
+                         "the Qwen3 model of the same widths (or of a Fagunex model beside the Lagulorn one) at two sizes, with the "
+                         "time of every kernel of one step of each kind")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -505,7 +540,7 @@ def main() -> int:
     cfg, CONTEXT, shape_batch = SHAPES[args.shape]
     if args.designs:
         torch.cuda.set_device(0)
-        side_by_side = lagulorn_side_by_side if args.designs == "lagulorn" else designs_side_by_side
+        side_by_side = {"lagulorn": lagulorn_side_by_side, "fagunex": fagunex_side_by_side}.get(args.designs, designs_side_by_side)
         print(json.dumps(side_by_side(q, torch, Sampler, min(args.steps, 64), warmup, args.batch or 8, args.context or 4096)))
         return 0
     if args.products:

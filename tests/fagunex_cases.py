@@ -122,7 +122,7 @@ def lively_weights(specs, seed):
 def decide_routers(tensors, seed):
     """Make the SET of chosen experts the same for every token, so that no rounded input can change it, while their
     weights still follow the token: the first value of the feed-forward's input is made the constant 1 (its norm's weight
-    0, its offset 1), the routers' first column puts the experts 1.5 apart in some order, and the rest of the router is
+    0, its offset 1), the routers' first column puts the experts 2 apart in some order, and the rest of the router is
     made small.  What a comparison in bfloat16 needs, where a close call would otherwise go either way."""
     import torch
     gen = torch.Generator().manual_seed(seed)
@@ -130,9 +130,9 @@ def decide_routers(tensors, seed):
         if not key.endswith(".mlp.router"):
             continue
         prefix = key[:-len("mlp.router")]
-        w = tensors[key].float() * 0.25
+        w = tensors[key].float() * 0.08
         n = w.shape[0]
-        w[:, 0] = 1.5 * torch.randperm(n, generator=gen).float() - 0.75 * n
+        w[:, 0] = 2.0 * torch.randperm(n, generator=gen).float() - n
         tensors[key] = w.to(torch.bfloat16)
         tensors[prefix + "norm2"][0] = 0.0
         tensors[prefix + "norm2.b"][0] = 1.0
