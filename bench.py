@@ -450,15 +450,18 @@ def lagulorn_side_by_side(q, torch, Sampler, steps, warmup, batch=8, context=409
 
 def fagunex_config(width, heads, d, ff, layers, window=1024, experts=16, top=2):
     """A Fagunex model of the widths of the Lagulorn model beside it: latent attention with a window, with queries through
-    a latent, a sink and an output gate; the gated recurrence (heads of d x d); latent attention over every earlier key;
-    the recurrence again; and so on.  A cache row is a latent of 4 d values and d / 2 rotated ones for all heads together.
-    Every layer's feed-forward is routed (`experts` experts of ff / (2 top), `top` per token) with a shared expert of the same
-    size beside them; a token side input of 64 values per layer."""
+    a latent, a sink and an output gate; the gated recurrence (width / d heads of d x d); latent attention over every earlier
+    key; the recurrence again; and so on.  The attention layers have 16 heads with plain keys of d values, d / 2 rotated ones
+    and values of width / 16; a cache row is a latent of 1.5 d values and the d / 2 rotated ones for all heads together (256
+    values at d = 128 where the Lagulorn layer beside it caches 3,072 a token).  Every layer's feed-forward is routed (`experts`
+    experts of ff / (2 top), `top` per token) with a shared expert of the same size beside them; a token side input of 64
+    values per layer."""
+    h = min(heads, 16)
     rot = {"base": 1000000.0, "dims": d // 2}
-    latent = {"heads": heads, "dim": d, "rot_dim": d // 2, "vdim": d, "kv_rank": 4 * d, "scale": (d + d // 2) ** -0.5, "rot": rot}
+    latent = {"heads": h, "dim": d, "rot_dim": d // 2, "vdim": width // h, "kv_rank": 3 * d // 2, "scale": (d + d // 2) ** -0.5, "rot": rot}
     first = {"type": "latent_attention", "mixer": dict(latent, q_rank=width * 3 // 4, mask={"size": window})}
     second = {"type": "latent_attention_2", "mixer": dict(latent)}
-    recurrent = {"type": "hgrn2", "mixer": {"heads": heads, "dim": d, "vdim": d}}
+    recurrent = {"type": "hgrn2", "mixer": {"heads": width // d, "dim": d, "vdim": d}}
     moe = {"kind": "moe", "expert": {"ff": ff // (2 * top)}, "router": {"experts": experts, "top": top}, "shared": {"ff": ff // (2 * top)}}
     order = [first, recurrent, second, recurrent]
     return {"architecture": "Fagunex", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-6}, "token_side": {"dim": 64},

@@ -359,7 +359,7 @@ def planted_latent_inputs(rng, w, p, m, width, lengths, backs, eps, peak):
 @pytest.mark.parametrize("kind,heads,d,r,vd,rank,q_rank,window,dims", [
     ("latent_attention", 2, 32, 8, 16, 48, None, 70, 8), ("latent_attention", 3, 32, 4, 40, 40, 120, 64, 2),
     ("latent_attention_2", 2, 48, 16, 24, 64, None, None, 16), ("latent_attention", 4, 32, 16, 32, 112, None, 200, 16),
-    ("latent_attention", 1, 64, 2, 8, 72, None, 1, 2)])
+    ("latent_attention", 1, 64, 2, 8, 88, None, 1, 2)])
 def test_latent_attention_with_keys_that_stand_out(tmp_path, dtype, kind, heads, d, r, vd, rank, q_rank, window, dims):
     """One layer inside an engine.  Every query points at ONE earlier key whose score then dominates: itself, the key
     before, keys at page borders, just inside and just outside the window, the first tokens, far back.  One head's sink
