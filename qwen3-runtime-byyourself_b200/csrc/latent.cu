@@ -15,8 +15,9 @@
 //   latent_queries : per (token, head).  The rotated part of the query is rotated and put behind the absorbed part
 //                    in the row the attention reads: q_full[t, h, rank:] = rotate(q[t, h, dim:]).
 //   head_product   : out[t, h, out_off + j] = sum_i x[t, h, x_off + i] * W[h, i, j]  (* sigmoid(gate[t, h, j])), a product
-//                    per head with 32-bit accumulation in ascending i: the absorption of W_uk into the query
-//                    and the expansion of the attention's output by W_uv (with the output gate on the way).
+//                    per head with 32-bit accumulation: the absorption of W_uk into the query and the expansion of
+//                    the attention's output by W_uv (with the output gate on the way).  bfloat16 operands whose rows
+//                    split into 16-byte packets take tensor-core tiles, everything else fmaf tiles.
 //
 // The rotation turns the first `rot_dims` values of the rotated part, in pairs (2i, 2i + 1) if `interleaved`, else
 // (i, i + rot_dims / 2); pair i of a token at position p is turned by the angle p * f_i, whose cosine and sine come
@@ -168,6 +169,119 @@ head_product_kernel(const T* __restrict__ x, int64_t x_row, int x_head, int x_of
     }
 }
 
+
+// The same product on the tensor cores, for bfloat16 operands whose rows can be fetched in 16-byte packets.  One block per
+// (64 tokens, head, 64 outputs); four warps of 16 tokens x 64 outputs each.  x and W pass through shared memory in chunks of
+// 64 inner values (two stages of asynchronous copies), fragments come from ldmatrix (W transposed on the way), sums are
+// 32-bit in mma.m16n8k16.  Packets beyond the last token, inner value or output are zero.
+constexpr int CM = 64, CN = 64, CK = 64, C_ROW = CK * 2 + 16;       // padded rows: conflict-free ldmatrix
+
+__device__ __forceinline__ void hp_cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
+}
+__device__ __forceinline__ void hp_ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void hp_ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void hp_mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(128)
+head_product_tc_kernel(const bf16* __restrict__ x, int64_t x_row, int x_head, int x_off, const bf16* __restrict__ w,
+                       bf16* __restrict__ out, int64_t out_row, int out_head, int out_off, const bf16* __restrict__ gate,
+                       int64_t gate_row, int64_t n_tokens, int K, int N) {
+    __shared__ __align__(16) unsigned char xs[2][CM * C_ROW];
+    __shared__ __align__(16) unsigned char ws[2][CK * C_ROW];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int head = blockIdx.y, col0 = blockIdx.z * CN;
+    const int64_t row0 = (int64_t)blockIdx.x * CM;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bf16* xh = x + (int64_t)head * x_head + x_off;
+    const bf16* wh = w + (int64_t)head * K * N;
+    const uint32_t xs_base = (uint32_t)__cvta_generic_to_shared(&xs[0][0]);
+    const uint32_t ws_base = (uint32_t)__cvta_generic_to_shared(&ws[0][0]);
+
+    auto issue = [&](int chunk, int stage) {
+        const int k0 = chunk * CK;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int piece = tid + e * 128, r = piece >> 3, c = piece & 7;       // 8 packets of 8 values a row
+            const uint32_t off = (uint32_t)(stage * CM * C_ROW + r * C_ROW + c * 16);
+            if (row0 + r < n_tokens && k0 + c * 8 < K) hp_cp_async16(xs_base + off, xh + (row0 + r) * x_row + k0 + c * 8);
+            else *reinterpret_cast<uint4*>(&xs[0][0] + off) = make_uint4(0, 0, 0, 0);
+            if (k0 + r < K && col0 + c * 8 < N) hp_cp_async16(ws_base + off, wh + (int64_t)(k0 + r) * N + col0 + c * 8);
+            else *reinterpret_cast<uint4*>(&ws[0][0] + off) = make_uint4(0, 0, 0, 0);
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+
+    float acc[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.0f;
+    const int chunks = (K + CK - 1) / CK;
+    issue(0, 0);
+    for (int c = 0; c < chunks; ++c) {
+        const int stage = c & 1;
+        if (c + 1 < chunks) {
+            issue(c + 1, stage ^ 1);
+            asm volatile("cp.async.wait_group 1;\n" ::);
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::);
+        }
+        __syncthreads();
+        const uint32_t xa = xs_base + stage * CM * C_ROW + (warp * 16 + (lane & 15)) * C_ROW + (lane >> 4) * 16;
+        const uint32_t wb = ws_base + stage * CK * C_ROW + ((lane & 7) + (((lane >> 3) & 1) << 3)) * C_ROW + (lane >> 4) * 16;
+        const int steps = min(CK, K - c * CK + 15) >> 4;
+        for (int kt = 0; kt < steps; ++kt) {
+            uint32_t a[4];
+            hp_ldmatrix_x4(a, xa + kt * 32);
+#pragma unroll
+            for (int n = 0; n < 8; n += 2) {
+                uint32_t b[4];
+                hp_ldmatrix_x4_trans(b, wb + kt * 16 * C_ROW + n * 16);
+                hp_mma_bf16(acc[n], a, b[0], b[1]);
+                hp_mma_bf16(acc[n + 1], a, b[2], b[3]);
+            }
+        }
+        __syncthreads();            // the stage may be overwritten by the next issue
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int64_t r = row0 + warp * 16 + (lane >> 2) + half * 8;
+        if (r >= n_tokens) continue;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            const int cc = col0 + n * 8 + (lane & 3) * 2;
+            if (cc >= N) continue;
+            float v0 = acc[n][half * 2], v1 = acc[n][half * 2 + 1];
+            if (gate != nullptr) {
+                const bf16* g = gate + r * gate_row + (int64_t)head * N + cc;
+                v0 = v0 / (1.0f + expf(-__bfloat162float(g[0])));
+                v1 = v1 / (1.0f + expf(-__bfloat162float(g[1])));
+            }
+            *reinterpret_cast<__nv_bfloat162*>(out + r * out_row + (int64_t)head * out_head + out_off + cc) = __floats2bfloat162_rn(v0, v1);
+        }
+    }
+}
+
+// whether the tensor-core form can take these operands: 16-byte packets of x and W, pairs of outputs
+template <typename T>
+static bool head_product_tiles(const void*, int64_t, int, int, const void*, const void*, int64_t, int, int, int, int) { return false; }
+template <>
+bool head_product_tiles<bf16>(const void* x, int64_t x_row, int x_head, int x_off, const void* w, const void* out, int64_t out_row,
+                              int out_head, int out_off, int K, int N) {
+    return K % 8 == 0 && N % 8 == 0 && x_row % 8 == 0 && x_head % 8 == 0 && x_off % 8 == 0 && ((uintptr_t)x & 15) == 0 &&
+           ((uintptr_t)w & 15) == 0 && out_row % 2 == 0 && out_head % 2 == 0 && out_off % 2 == 0 && ((uintptr_t)out & 3) == 0;
+}
+
 }  // namespace
 
 #define Q3_LATENT_EXPORTS(SUFFIX, T)                                                                                        \
@@ -208,6 +322,12 @@ head_product_kernel(const T* __restrict__ x, int64_t x_row, int x_head, int x_of
         if (heads <= 0 || heads > 65535 || K <= 0 || N <= 0 || (N + TN - 1) / TN > 65535 ||                                  \
             (n_tokens + TM - 1) / TM > 0x7fffffffLL)                                                                        \
             return Q3_ERR_BAD_SIZE;                                                                                         \
+        if (head_product_tiles<T>(x, x_row, x_head, x_off, w, out, out_row, out_head, out_off, K, N)) {                      \
+            const dim3 tiles((unsigned)((n_tokens + CM - 1) / CM), heads, (N + CN - 1) / CN);                                \
+            return (int)q3_launch(head_product_tc_kernel, tiles, dim3(128), 0, (cudaStream_t)stream, (const bf16*)x, x_row,  \
+                                  x_head, x_off, (const bf16*)w, (bf16*)out, out_row, out_head, out_off, (const bf16*)gate,  \
+                                  gate_row, n_tokens, K, N);                                                                 \
+        }                                                                                                                   \
         const dim3 grid((unsigned)((n_tokens + TM - 1) / TM), heads, (N + TN - 1) / TN);                                     \
         return (int)q3_launch(head_product_kernel<T>, grid, dim3(256), 0, (cudaStream_t)stream, (const T*)x, x_row, x_head,  \
                               x_off, (const T*)w, (T*)out, out_row, out_head, out_off, (const T*)gate, gate_row, n_tokens, K, \

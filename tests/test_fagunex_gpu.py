@@ -233,6 +233,32 @@ def test_product_per_head_with_and_without_the_gate(dtype, heads, K, N):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,K,N,rows", [(3, 48, 72, 150), (2, 128, 192, 70), (16, 200, 40, 9), (1, 8, 8, 64), (2, 72, 136, 129),
+                                            (5, 64, 64, 1)])
+def test_product_per_head_on_rows_that_split_into_packets(dtype, heads, K, N, rows):
+    """Sizes and views the tensor-core tiles take in bfloat16: every offset a multiple of 8 values, tokens and outputs that
+    do not fill the last tile, inner sizes that end inside a chunk and inside a step."""
+    import torch
+    from qwen3_b200.csrc import ops
+    rng = np.random.default_rng(K + N + rows)
+    T = torch_dtype(dtype)
+    wide = dev(rng.standard_normal((rows, 8 + heads * (K + 16) + heads * N)), T)
+    x = wide[:, 8:8 + heads * (K + 16)]                                 # per head: 8 values that are not read, K, 8 more
+    gate = wide[:, 8 + heads * (K + 16):]
+    w = dev(rng.standard_normal((heads, K, N)) / K ** 0.5, T)
+    want = np.einsum("thk,hkn->thn", f64(x).reshape(rows, heads, K + 16)[:, :, 8:8 + K], f64(w))
+    out = torch.full((rows, heads * (N + 4)), 5.0, dtype=T, device="cuda")
+    tol = 2e-5 if dtype == "float32" else 3e-2
+    ops.head_product(x, K + 16, 8, w, out, N + 4, 2, rows)
+    got = f64(out).reshape(rows, heads, N + 4)
+    assert np.allclose(got[:, :, 2:N + 2], want, atol=tol) and np.all(got[:, :, :2] == 5.0) and np.all(got[:, :, N + 2:] == 5.0)
+    ops.head_product(x, K + 16, 8, w, out, N + 4, 2, rows, gate=gate)
+    got = f64(out).reshape(rows, heads, N + 4)
+    assert np.allclose(got[:, :, 2:N + 2], want * plain.sigmoid(f64(gate).reshape(rows, heads, N)), atol=tol)
+    assert np.all(got[:, :, :2] == 5.0) and np.all(got[:, :, N + 2:] == 5.0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("rank,rot,dims,interleaved,q_rank", [(20, 6, 6, True, 10), (24, 8, 8, False, 0), (40, 8, 4, True, 0),
                                                               (13, 2, 2, False, 3), (112, 16, 16, True, 48), (9, 0, 0, False, 0)])
 def test_latent_rows_are_normed_rotated_and_written_to_their_pages(dtype, rank, rot, dims, interleaved, q_rank):
