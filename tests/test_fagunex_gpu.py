@@ -676,6 +676,23 @@ def test_greedy_generation_through_the_entry_point(folders, name):
     assert [r.token_ids for r in again] == [r.token_ids for r in got]
 
 
+def test_the_command_line_generates_from_token_ids(folders):
+    """bin/qwen3_chat on a Fagunex folder: the model class comes from config.json; greedy sampling through the scheduler."""
+    import subprocess
+    import sys
+    folder, weights = folders["A", "float32"]
+    cfg = case("A")
+    prompts = [[7, 8, 9, 150, 2], [100, 3]]
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "qwen3_chat"), folder, "--greedy", "--dtype", "float32",
+                          "--max-new-tokens", "9", "--max-context", "64", "--tokens", "7,8,9,150,2", "--tokens", "100 3"],
+                         capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [l for l in out.stdout.strip().splitlines() if l and l[0].isdigit()]
+    assert len(lines) == 2
+    for p, line in zip(prompts, lines):
+        assert [int(t) for t in line.split("#")[0].strip().split(",")] == plain.generate_greedy(cfg, weights, p, 9)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_trace_replay_from_the_command_line(tmp_path, folders, dtype, monkeypatch):
     from test_trace_run_gpu import replay
