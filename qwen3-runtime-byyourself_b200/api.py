@@ -17,7 +17,7 @@ from dataclasses import dataclass, field
 from typing import List, Optional, Sequence
 
 from .cache import PAGE_TOKENS, CacheError, CacheFull, CacheNeed
-from .config import (ConfigError, DozazenConfig, FagunexConfig, LagulornConfig, LayerSpec, ModelPlan, PartSpec, Qwen3Config, StreamStep, config_from_dict,
+from .config import (ConfigError, DozazenConfig, FagunexConfig, FedinexConfig, LagulornConfig, LayerSpec, ModelPlan, PartSpec, Qwen3Config, StreamStep, config_from_dict,
                      known_architectures, load_config, register_architecture)
 from .engine.engine import Engine, StepEntry, StepError
 from .engine.generate import MAX_NEW_TOKENS, STOP_TOKEN, GenerationResult, generate, plan_batches
@@ -49,7 +49,7 @@ def generate_token_ids(engine: Engine, prompts: Sequence[Sequence[int]], samplin
 
 __all__ = [
     "PAGE_TOKENS", "CacheError", "CacheFull", "CacheNeed", "ConfigError", "LayerSpec", "ModelPlan", "PartSpec",
-    "Qwen3Config", "DozazenConfig", "LagulornConfig", "FagunexConfig", "StreamStep", "config_from_dict", "known_architectures", "load_config", "register_architecture", "Engine",
+    "Qwen3Config", "DozazenConfig", "LagulornConfig", "FagunexConfig", "FedinexConfig", "StreamStep", "config_from_dict", "known_architectures", "load_config", "register_architecture", "Engine",
     "StepEntry", "StepError", "MAX_NEW_TOKENS", "STOP_TOKEN", "GenerationResult", "generate", "plan_batches",
     "build_model", "register_part", "SamplingParams", "uniform_for", "SafetensorsFormatError", "WeightError",
     "WeightSpec", "load_weights", "random_weights", "save_file", "write_model_folder", "write_random_model",

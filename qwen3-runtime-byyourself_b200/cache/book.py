@@ -36,7 +36,8 @@ class CacheNeed:
     `value_dim` is the size of a value row where it differs from the key's `head_dim`;
     `value_heads` the number of value heads where it differs from `num_kv_heads` (values
     that several key heads share).  `block_state` is a second float32 area per sequence, of that many values, for
-    what the layer's block keeps from token to token beside its mixer's state (empty: 0).
+    what the layer's block keeps from token to token beside its mixer's state (empty: 0).  `keep_first` (kind 'window'):
+    every query also reads the first so many keys of its sequence, whose pages are therefore never given back.
     """
     kind: str = "none"
     num_kv_heads: int = 0
@@ -46,6 +47,7 @@ class CacheNeed:
     value_dim: Optional[int] = None
     value_heads: Optional[int] = None
     block_state: int = 0
+    keep_first: int = 0
 
     def __post_init__(self):
         if self.kind not in ("full", "window", "chunk", "none"):
@@ -57,7 +59,8 @@ class CacheNeed:
 
     def group_key(self):
         return (self.kind, self.num_kv_heads, self.head_dim, self.window if self.kind in ("window", "chunk") else None,
-                self.value_dim or self.head_dim, self.value_heads or self.num_kv_heads)
+                self.value_dim or self.head_dim, self.value_heads or self.num_kv_heads,
+                self.keep_first if self.kind == "window" else 0)
 
 
 class CacheError(RuntimeError):
@@ -77,7 +80,7 @@ def _host():
         i32p, i64p = ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int64)
         lib.q3_host_last_error.restype = ctypes.c_char_p
         lib.q3_book_create.argtypes = [i32p, i32p, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_int,
-                                       ctypes.POINTER(ctypes.c_void_p)]
+                                       ctypes.POINTER(ctypes.c_void_p), i32p]
         lib.q3_book_destroy.argtypes = [ctypes.c_void_p]
         lib.q3_book_destroy.restype = None
         lib.q3_book_info.argtypes = [ctypes.c_void_p, i32p]
@@ -193,9 +196,10 @@ class CacheBook:
         G = len(group_needs)
         kinds = (ctypes.c_int32 * max(G, 1))(*[{"window": 1, "chunk": 2}.get(n.kind, 0) for n in group_needs])
         windows = (ctypes.c_int32 * max(G, 1))(*[int(n.window or 0) for n in group_needs])
+        keeps = (ctypes.c_int32 * max(G, 1))(*[int(n.keep_first or 0) for n in group_needs])
         handle = ctypes.c_void_p()
         code = _host().q3_book_create(kinds, windows, G, int(max_tokens), int(max_seq_len), int(n_slots or 0), PAGE_TOKENS,
-                                      ctypes.byref(handle))
+                                      ctypes.byref(handle), keeps)
         if code:
             _raise(code)
         self._handle = handle

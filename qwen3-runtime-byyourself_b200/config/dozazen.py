@@ -63,6 +63,10 @@ def _typed(v, kind, name: str):
         if not isinstance(v, str):
             raise ConfigError(f"config field '{name}' must be a string")
         return v
+    if kind is bool:
+        if not isinstance(v, bool):
+            raise ConfigError(f"config field '{name}' must be true or false")
+        return v
     raise TypeError(kind)
 
 

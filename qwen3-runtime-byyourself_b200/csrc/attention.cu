@@ -244,7 +244,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
                          T* __restrict__ out, const int* __restrict__ token_seq, const int* __restrict__ token_pos,
                          const int* __restrict__ page_table, int pages_per_seq, int nq, int nkv, int d, float scale,
                          int window, int vd, float softcap, int chunk, int sink, int nv, int out_f32,
-                         const float* __restrict__ sink_values) {
+                         const float* __restrict__ sink_values, int keep_first) {
     __shared__ float q_s[GENERIC_KEY_DIM];
     __shared__ float score[PAGE];
     __shared__ float prob[PAGE];
@@ -265,23 +265,28 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
     float m_run = sink ? (sink_values ? sink_values[head] : 0.0f) : -INFINITY, l_run = sink ? 1.0f : 0.0f;
     float acc[GENERIC_VALUE_DIM / 128] = {};
     const float inv_cap = softcap > 0.0f ? 1.0f / softcap : 0.0f;
-    for (int pg = lo / PAGE; pg <= pos / PAGE; ++pg) {
+    // with a window, the first `keep_first` keys of the sequence stay visible: their pages come first, then the window's
+    const int keep = window > 0 ? keep_first : 0;
+    for (int pg = 0; pg <= pos / PAGE; ++pg) {
+        if (pg < lo / PAGE && pg * PAGE >= keep) continue;          // nothing of this page is seen (it may be given back)
         const T* kp = k_pages + ((int64_t)pages[pg] * nkv + kvh) * PAGE * d;
         const T* vp = v_pages + ((int64_t)pages[pg] * nv + vh) * PAGE * vd;
-        const int j_lo = max(lo - pg * PAGE, 0), j_hi = min(pos - pg * PAGE, PAGE - 1);  // inclusive, in-page
+        const int j_hi = min(pos - pg * PAGE, PAGE - 1);            // inclusive, in-page
+        const int j_lo = pg * PAGE < keep ? 0 : max(lo - pg * PAGE, 0);
+        const int gap_lo = keep - pg * PAGE, gap_hi = lo - pg * PAGE;   // keys j with gap_lo <= j < gap_hi are not seen
         for (int j = warp; j < PAGE; j += 4) {
             float dot = 0.0f;
-            if (j >= j_lo && j <= j_hi) {
+            if (j >= j_lo && j <= j_hi && !(j >= gap_lo && j < gap_hi)) {
                 for (int i = lane; i < d; i += 32) dot = fmaf(q_s[i], to_f32<T>(kp[(int64_t)j * d + i]), dot);
             }
             dot = warp_sum(dot) * scale;
             if (softcap > 0.0f) dot = softcap * tanhf(dot * inv_cap);
-            if (lane == 0) score[j] = (j >= j_lo && j <= j_hi) ? dot : -INFINITY;
+            if (lane == 0) score[j] = (j >= j_lo && j <= j_hi && !(j >= gap_lo && j < gap_hi)) ? dot : -INFINITY;
         }
         __syncthreads();
         float m_new = m_run;
         for (int j = 0; j < PAGE; ++j) m_new = fmaxf(m_new, score[j]);
-        if (tid < PAGE) prob[tid] = (tid >= j_lo && tid <= j_hi) ? expf(score[tid] - m_new) : 0.0f;
+        if (tid < PAGE) prob[tid] = score[tid] > -INFINITY ? expf(score[tid] - m_new) : 0.0f;
         __syncthreads();
         const float alpha = expf(m_run - m_new);  // 0 on the first page (m_run = -inf, m_new finite)
         float l_add = 0.0f, v_add[GENERIC_VALUE_DIM / 128] = {};
@@ -347,17 +352,53 @@ template <typename T>
 int attention_generic_launch(const T* q, const T* k_pages, const T* v_pages, T* out, const int* token_seq,
                              const int* token_pos, const int* page_table, int pages_per_seq, int64_t n_tokens, int nq,
                              int nkv, int d, float scale, int window, int vd, float softcap, int chunk, int sink, int nv,
-                             int out_f32, const float* sink_values, cudaStream_t stream) {
+                             int out_f32, const float* sink_values, int keep_first, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (vd <= 0) vd = d;
     if (nv <= 0) nv = nkv;
     if (nkv <= 0 || nkv % nv != 0) return Q3_ERR_BAD_SIZE;
     if (d <= 0 || d > GENERIC_KEY_DIM || vd > GENERIC_VALUE_DIM || nq <= 0 || nkv <= 0 || nq % nkv != 0) return Q3_ERR_BAD_SIZE;
-    if (window > 0 && chunk > 0) return Q3_ERR_BAD_SIZE;
+    if ((window > 0 && chunk > 0) || keep_first < 0) return Q3_ERR_BAD_SIZE;
     if (n_tokens > 65535) return Q3_ERR_TOO_LARGE;
     const dim3 grid(nq, (unsigned)n_tokens);
     return (int)q3_launch(attention_generic_kernel<T>, grid, dim3(128), 0, stream, q, k_pages, v_pages, out, token_seq,
-                          token_pos, page_table, pages_per_seq, nq, nkv, d, scale, window, vd, softcap, chunk, sink, nv, out_f32, sink_values);
+                          token_pos, page_table, pages_per_seq, nq, nkv, d, scale, window, vd, softcap, chunk, sink, nv, out_f32, sink_values,
+                          keep_first);
+}
+
+// Values blended across layers, on the value columns of a projection's rows (in place): v <- v + bias first (if
+// any); the first layer of a chain keeps a copy, `first` [N, width]; a later one goes on with
+// v <- (1 - lambda) v + lambda first.  32-bit arithmetic, stored in T.
+template <typename T>
+__global__ void value_mix_kernel(T* __restrict__ rows, int64_t row, int64_t v_off, int width, const float* __restrict__ bias,
+                                 T* __restrict__ first, int save, float lambda, int64_t n_tokens) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t total = n_tokens * width;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = i / width;
+        const int c = (int)(i % width);
+        T* at = rows + t * row + v_off + c;
+        float v = to_f32<T>(*at);
+        if (bias != nullptr) v = round_to<T>(v + bias[c]);
+        if (save) first[i] = from_f32<T>(v);
+        else v = (1.0f - lambda) * v + lambda * to_f32<T>(first[i]);
+        *at = from_f32<T>(v);
+    }
+}
+
+// One sigmoid gate per (token, head) on the attention's output, in place: x[t, h, :] *= sigmoid(gate[t, h]).
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ x, const T* __restrict__ gate, int64_t gate_row, int heads, int vd, int64_t n_tokens) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t total = n_tokens * heads * vd;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t th = i / vd, t = th / heads;
+        const int h = (int)(th % heads);
+        const float z = to_f32<T>(gate[t * gate_row + h]);
+        x[i] = from_f32<T>(to_f32<T>(x[i]) / (1.0f + expf(-z)));
+    }
 }
 
 }  // namespace
@@ -378,11 +419,28 @@ int attention_generic_launch(const T* q, const T* k_pages, const T* v_pages, T* 
                                                 int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d,          \
                                                 float scale, int window, int value_dim, float softcap,     \
                                                 int chunk, int sink, int value_heads, int out_f32,                   \
-                                                const float* sink_values, void* stream) {                             \
+                                                const float* sink_values, int keep_first, void* stream) {             \
         return attention_generic_launch<T>((const T*)q, (const T*)k_pages, (const T*)v_pages, (T*)out, token_seq,     \
                                            token_pos, page_table, pages_per_seq, n_tokens, nq, nkv, d, scale, window, \
                                            value_dim, softcap, chunk, sink, value_heads, out_f32, sink_values,        \
-                                           (cudaStream_t)stream);                                                     \
+                                           keep_first, (cudaStream_t)stream);                                         \
+    }                                                                                                                 \
+    Q3_EXPORT int q3_value_mix_##SUFFIX(void* rows, int64_t row, int64_t v_off, int width, const float* bias,         \
+                                        void* first, int save, float lambda, int64_t n_tokens, void* stream) {        \
+        if (n_tokens <= 0) return 0;                                                                                  \
+        if (width <= 0 || v_off < 0 || v_off + width > row) return Q3_ERR_BAD_SIZE;                                   \
+        const int64_t blocks = (n_tokens * width + 255) / 256;                                                        \
+        return (int)q3_launch(value_mix_kernel<T>, dim3((unsigned)(blocks < 65536 ? blocks : 65536)), dim3(256), 0,   \
+                              (cudaStream_t)stream, (T*)rows, row, v_off, width, bias, (T*)first, save, lambda,       \
+                              n_tokens);                                                                              \
+    }                                                                                                                 \
+    Q3_EXPORT int q3_head_gate_##SUFFIX(void* x, const void* gate, int64_t gate_row, int heads, int vd,               \
+                                        int64_t n_tokens, void* stream) {                                             \
+        if (n_tokens <= 0) return 0;                                                                                  \
+        if (heads <= 0 || vd <= 0) return Q3_ERR_BAD_SIZE;                                                            \
+        const int64_t blocks = (n_tokens * heads * vd + 255) / 256;                                                   \
+        return (int)q3_launch(head_gate_kernel<T>, dim3((unsigned)(blocks < 65536 ? blocks : 65536)), dim3(256), 0,   \
+                              (cudaStream_t)stream, (T*)x, (const T*)gate, gate_row, heads, vd, n_tokens);            \
     }
 
 Q3_ATTENTION_EXPORTS(f32, float)

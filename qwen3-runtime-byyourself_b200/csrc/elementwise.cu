@@ -248,6 +248,67 @@ static int silu_mul_launch(const T* gate_up, T* out, int64_t rows, int inter, in
                           interleaved, act);
 }
 
+// ---------------------------------------------------------------- the clamped gated activation; a weighted sum
+// out = g sigmoid(alpha g) (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit); the layout of `silu_mul`.
+template <typename T, int VEC>
+__global__ void clamped_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int64_t rows, int inter, int interleaved,
+                                   float limit, float alpha) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t per_row = inter / VEC;
+    const int64_t total = rows * per_row;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / per_row;
+        const int c = (int)(i % per_row) * VEC;
+        float g[VEC], u[VEC];
+        const int64_t gate_at = interleaved ? (int64_t)(c >> 3) * 16 + (c & 7) : c;
+        const int64_t up_at = interleaved ? gate_at + 8 : (int64_t)inter + c;
+        load_vec<T, VEC>(gate_up + r * 2 * inter + gate_at, g);
+        load_vec<T, VEC>(gate_up + r * 2 * inter + up_at, u);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+            const float gc = fminf(g[k], limit), uc = fminf(fmaxf(u[k], -limit), limit);
+            g[k] = gc / (1.0f + expf(-alpha * gc)) * (uc + 1.0f);
+        }
+        store_vec<T, VEC>(out + r * inter + c, g);
+    }
+}
+
+template <typename T>
+static int clamped_mul_launch(const T* gate_up, T* out, int64_t rows, int inter, int interleaved, float limit, float alpha,
+                              cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (inter <= 0 || (interleaved && inter % 8 != 0)) return Q3_ERR_BAD_SIZE;
+    constexpr int V = Pack<T>::N;
+    const bool vec = inter % V == 0 && aligned16(gate_up) && aligned16(out);
+    const int64_t work = rows * (inter / (vec ? V : 1));
+    int64_t blocks = (work + 255) / 256;
+    const int64_t resident = (int64_t)q3_device_sm_count() * 16;
+    if (blocks > resident) blocks = resident;
+    if (vec)
+        return (int)q3_launch(clamped_mul_kernel<T, V>, dim3((unsigned)blocks), dim3(256), 0, stream, gate_up, out, rows, inter,
+                              interleaved, limit, alpha);
+    return (int)q3_launch(clamped_mul_kernel<T, 1>, dim3((unsigned)blocks), dim3(256), 0, stream, gate_up, out, rows, inter,
+                          interleaved, limit, alpha);
+}
+
+template <typename T>
+__global__ void scaled_sum_kernel(const T* a, const T* b, float sa, float sb, T* out, int64_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        out[i] = from_f32<T>(sa * to_f32<T>(a[i]) + sb * to_f32<T>(b[i]));
+}
+
+template <typename T>
+__global__ void add_bias_kernel(T* x, const float* __restrict__ bias, int64_t rows, int size) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t n = rows * size;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        x[i] = from_f32<T>(to_f32<T>(x[i]) + bias[i % size]);
+}
+
 // ---------------------------------------------------------------- gather rows (+ pending branch)
 // out[r] = x[idx[r]] (+ delta[idx[r]]): the rows whose logits are wanted, with the
 // last branch output added in 32-bit.
@@ -330,6 +391,24 @@ Q3_EXPORT int q3_place_rows(const void* src, int src_kind, void* dst, int dst_ki
     Q3_EXPORT int q3_act_mul_##SUFFIX(const void* gate_up, void* out, int64_t rows, int inter, int interleaved,     \
                                       int act, void* stream) {                                                      \
         return silu_mul_launch<T>((const T*)gate_up, (T*)out, rows, inter, interleaved, act, (cudaStream_t)stream); \
+    }                                                                                                               \
+    Q3_EXPORT int q3_clamped_mul_##SUFFIX(const void* gate_up, void* out, int64_t rows, int inter, int interleaved, \
+                                          float limit, float alpha, void* stream) {                                 \
+        return clamped_mul_launch<T>((const T*)gate_up, (T*)out, rows, inter, interleaved, limit, alpha,            \
+                                     (cudaStream_t)stream);                                                         \
+    }                                                                                                               \
+    Q3_EXPORT int q3_scaled_sum_##SUFFIX(const void* a, const void* b, float sa, float sb, void* out, int64_t n,    \
+                                         void* stream) {                                                            \
+        if (n <= 0) return 0;                                                                                       \
+        const int64_t blocks = (n + 255) / 256;                                                                     \
+        return (int)q3_launch(scaled_sum_kernel<T>, dim3((unsigned)(blocks < 65536 ? blocks : 65536)), dim3(256), 0, \
+                              (cudaStream_t)stream, (const T*)a, (const T*)b, sa, sb, (T*)out, n);                  \
+    }                                                                                                               \
+    Q3_EXPORT int q3_add_bias_##SUFFIX(void* x, const float* bias, int64_t rows, int size, void* stream) {          \
+        if (rows <= 0 || size <= 0) return 0;                                                                       \
+        const int64_t blocks = (rows * size + 255) / 256;                                                           \
+        return (int)q3_launch(add_bias_kernel<T>, dim3((unsigned)(blocks < 65536 ? blocks : 65536)), dim3(256), 0,  \
+                              (cudaStream_t)stream, (T*)x, bias, rows, size);                                       \
     }                                                                                                               \
     Q3_EXPORT int q3_gather_rows_##SUFFIX(const void* x, const void* delta, const int* idx, void* out, int64_t rows, \
                                           int size, void* stream) {                                                 \

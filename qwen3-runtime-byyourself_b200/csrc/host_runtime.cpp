@@ -44,12 +44,13 @@ Q3_HOST_EXPORT const char* q3_host_last_error() { return g_error.c_str(); }
 
 // kinds[g]: 0 = every key, 1 = a window of windows[g] keys, 2 = the keys of the query's own chunk of windows[g] positions.
 Q3_HOST_EXPORT int q3_book_create(const int* kinds, const int* windows, int n_groups, int64_t max_tokens, int64_t max_seq_len,
-                                  int n_slots, int page_tokens, void** out) {
+                                  int n_slots, int page_tokens, void** out, const int* keep_first) {
     return guarded([&] {
         std::vector<qwen3::GroupNeed> needs(n_groups);
         for (int g = 0; g < n_groups; ++g) {
             needs[g].kind = kinds[g] == 2 ? qwen3::GroupKind::Chunk : kinds[g] ? qwen3::GroupKind::Window : qwen3::GroupKind::Full;
             needs[g].window = windows[g];
+            needs[g].keep_first = keep_first != nullptr ? keep_first[g] : 0;
         }
         *out = new qwen3::CacheBook(needs, max_tokens, max_seq_len, n_slots, page_tokens);
     });

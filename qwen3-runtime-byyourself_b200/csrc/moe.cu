@@ -7,8 +7,9 @@
 //                 the `top` largest choice scores win (ties: the lower index); the weights are their plain
 //                 scores s.  The last `identity` outputs are experts without tensors whose output is the
 //                 token itself: their weights are summed into id_weight[token].
-//                 `by_logit`: the `top` largest logits win instead and the weights are the softmax over the chosen
-//                 logits only.  With `gate_out`, the router matrix has one more row after the outputs whose logit
+//                 `by_logit` 1: the `top` largest logits win instead and the weights are the softmax over the chosen
+//                 logits only; 2: the scores are sigmoid(z), each output by itself.  `group_pair`: a group's score is
+//                 the sum of its two largest choice scores.  The weights are multiplied by `weight_scale`.  With `gate_out`, the router matrix has one more row after the outputs whose logit
 //                 is no expert's: gate_out[token] = sigmoid(that logit), the weight of a shared expert.
 //   moe_sort    : one block.  Counts the (token, choice) pairs of every real expert, lays the experts out one
 //                 after the other (offsets) and gives every pair its place (slot_of_pair, pair_of_slot).
@@ -34,7 +35,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const T* __restrict__ h, const T* __restrict__ w_router, const float* __restrict__ correction,
                  int* __restrict__ top_ids, float* __restrict__ top_w, float* __restrict__ id_weight, int hidden, int n_out,
-                 int n_real, int top, int group_count, int group_keep, int by_logit, float* __restrict__ gate_out) {
+                 int n_real, int top, int group_count, int group_keep, int by_logit, float* __restrict__ gate_out, int group_pair,
+                 float weight_scale) {
     __shared__ float z[MAX_OUTPUTS];
     __shared__ float choice[MAX_OUTPUTS];
     __shared__ float group_best[MAX_OUTPUTS];
@@ -66,7 +68,7 @@ moe_route_kernel(const T* __restrict__ h, const T* __restrict__ w_router, const 
     __syncthreads();
     if (tid != 0) return;
     if (gate_out != nullptr) gate_out[t] = 1.0f / (1.0f + expf(-z[n_out]));
-    if (by_logit) {
+    if (by_logit == 1) {
         // the largest logits (ties: the lower index), weighted by the softmax over the chosen logits alone
         float best_z = 0.0f, sum = 0.0f;
         for (int e = 0; e < n_out; ++e) choice[e] = z[e];
@@ -91,24 +93,40 @@ moe_route_kernel(const T* __restrict__ h, const T* __restrict__ w_router, const 
         id_weight[t] = idw;
         return;
     }
-    float m = -INFINITY, sum = 0.0f;
-    for (int e = 0; e < n_out; ++e) m = fmaxf(m, z[e]);
-    for (int e = 0; e < n_out; ++e) {
-        z[e] = expf(z[e] - m);
-        sum += z[e];
-    }
-    const float inv = 1.0f / sum;
-    for (int e = 0; e < n_out; ++e) {
-        z[e] *= inv;
-        choice[e] = z[e] + correction[e];
+    if (by_logit == 2) {                         // every output's score by itself: sigmoid(z)
+        for (int e = 0; e < n_out; ++e) {
+            z[e] = 1.0f / (1.0f + expf(-z[e]));
+            choice[e] = z[e] + correction[e];
+        }
+    } else {
+        float m = -INFINITY, sum = 0.0f;
+        for (int e = 0; e < n_out; ++e) m = fmaxf(m, z[e]);
+        for (int e = 0; e < n_out; ++e) {
+            z[e] = expf(z[e] - m);
+            sum += z[e];
+        }
+        const float inv = 1.0f / sum;
+        for (int e = 0; e < n_out; ++e) {
+            z[e] *= inv;
+            choice[e] = z[e] + correction[e];
+        }
     }
     if (group_count > 1) {
-        // a group's score is its best choice score; the `keep` best groups stay (of equal groups the earlier one)
+        // a group's score is its best choice score, or (`group_pair`) the sum of its two best; the `keep` best groups
+        // stay (of equal groups the earlier one)
         const int size = n_out / group_count;
         for (int g = 0; g < group_count; ++g) {
-            float best = -INFINITY;
-            for (int e = 0; e < size; ++e) best = fmaxf(best, choice[g * size + e]);
-            group_best[g] = best;
+            float best = -INFINITY, second = -INFINITY;
+            for (int e = 0; e < size; ++e) {
+                const float c = choice[g * size + e];
+                if (c > best) {
+                    second = best;
+                    best = c;
+                } else if (c > second) {
+                    second = c;
+                }
+            }
+            group_best[g] = group_pair && size > 1 ? best + second : best;
             group_kept[g] = 0;
         }
         for (int k = 0; k < group_keep; ++k) {
@@ -128,8 +146,8 @@ moe_route_kernel(const T* __restrict__ h, const T* __restrict__ w_router, const 
         if (best < 0) best = 0;                  // fewer candidates than `top` (the caller's sizes rule it out)
         choice[best] = -INFINITY;
         top_ids[t * top + k] = best;
-        top_w[t * top + k] = z[best];
-        if (best >= n_real) idw += z[best];
+        top_w[t * top + k] = z[best] * weight_scale;
+        if (best >= n_real) idw += z[best] * weight_scale;
     }
     id_weight[t] = idw;
 }
@@ -496,7 +514,7 @@ int moe_experts_launch(const T* h, const T* w_gate_up, const T* w_down, const in
     Q3_EXPORT int q3_moe_route_##SUFFIX(const void* h, const void* w_router, const float* correction, int* top_ids,       \
                                         float* top_w, float* id_weight, int64_t n_tokens, int hidden, int n_out, int n_real, \
                                         int top, int group_count, int group_keep, int by_logit, float* gate_out,           \
-                                        void* stream) {                                                                   \
+                                        int group_pair, float weight_scale, void* stream) {                                                                   \
         if (n_tokens <= 0) return 0;                                                                                      \
         if (n_out <= 0 || n_out >= MAX_OUTPUTS || top <= 0 || top > n_out || n_real < 0 || n_real > n_out || \
             group_count <= 0 || n_out % group_count != 0 || group_keep <= 0 || group_keep > group_count ||                \
@@ -504,7 +522,7 @@ int moe_experts_launch(const T* h, const T* w_gate_up, const T* w_down, const in
             return Q3_ERR_BAD_SIZE;                                                                                       \
         return (int)q3_launch(moe_route_kernel<T>, dim3((unsigned)n_tokens), dim3(256), 0, (cudaStream_t)stream,          \
                               (const T*)h, (const T*)w_router, correction, top_ids, top_w, id_weight, hidden, n_out,      \
-                              n_real, top, group_count, group_keep, by_logit, gate_out);                                  \
+                              n_real, top, group_count, group_keep, by_logit, gate_out, group_pair, weight_scale);        \
     }                                                                                                                     \
     Q3_EXPORT int q3_moe_experts_##SUFFIX(const void* h, const void* w_gate_up, const void* w_down, const int* offsets,   \
                                           const int* pair_of_slot, void* act, float* y, int n_pairs, int n_real, int top, \

@@ -242,6 +242,37 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False
     return out
 
 
+def clamped_mul(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float, interleaved: bool = False) -> torch.Tensor:
+    """out[r, c] = g sigmoid(alpha g) (u + 1) with g = min(gate[r, c], limit), u = clamp(up[r, c], -limit, limit); `gate_up`
+    laid out as for `silu_mul`."""
+    s = _suffix(gate_up)
+    rows, two_i = gate_up.shape
+    if two_i % 2 or out.shape != (rows, two_i // 2) or out.dtype != gate_up.dtype:
+        raise KernelError("clamped_mul: output does not fit")
+    fn = _fn("elementwise.cu", f"q3_clamped_mul_{s}", [c_void_p, c_void_p, c_int64, c_int, c_int, c_float, c_float, c_void_p])
+    _check(fn(_dev(gate_up, "gate_up"), _dev(out, "out"), rows, two_i // 2, int(bool(interleaved)), float(limit), float(alpha),
+              _stream()), "clamped_mul")
+    return out
+
+
+def scaled_sum(a: torch.Tensor, b: torch.Tensor, scale_a: float, scale_b: float, out: torch.Tensor) -> torch.Tensor:
+    """out = scale_a * a + scale_b * b elementwise, in 32-bit, stored in the tensors' type (`out` may be `a` or `b`)."""
+    if a.shape != b.shape or out.shape != a.shape or a.dtype != b.dtype or out.dtype != a.dtype:
+        raise KernelError("scaled_sum: shapes do not fit")
+    fn = _fn("elementwise.cu", f"q3_scaled_sum_{_suffix(a)}", [c_void_p, c_void_p, c_float, c_float, c_void_p, c_int64, c_void_p])
+    _check(fn(_dev(a, "a"), _dev(b, "b"), float(scale_a), float(scale_b), _dev(out, "out"), a.numel(), _stream()), "scaled_sum")
+    return out
+
+
+def add_bias(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """x[r, c] += bias[c] in place (32-bit sum, stored in x's type); bias float32."""
+    if bias.numel() != x.shape[-1]:
+        raise KernelError("add_bias: one value per column")
+    fn = _fn("elementwise.cu", f"q3_add_bias_{_suffix(x)}", [c_void_p, c_void_p, c_int64, c_int, c_void_p])
+    _check(fn(_dev(x, "x"), _dev(bias, "bias", torch.float32), x.numel() // x.shape[-1], x.shape[-1], _stream()), "add_bias")
+    return x
+
+
 def gather_rows(x: torch.Tensor, idx: torch.Tensor, out: torch.Tensor, delta: Optional[torch.Tensor] = None):
     """out[r] = x[idx[r]] (+ delta[idx[r]], summed in 32-bit)."""
     s = _suffix(x)
@@ -416,8 +447,9 @@ def _sink_ptr(sink, sink_values, nq: int):
 def attention_generic(q, k_pages, v_pages, out, token_seq, token_pos, page_table, n_tokens: int, nq: int, nkv: int,
                       d: int, scale: float, window: Optional[int] = None, value_dim: Optional[int] = None,
                       softcap: float = 0.0, chunk: Optional[int] = None, sink: bool = False, value_heads: Optional[int] = None,
-                      sink_values: Optional[torch.Tensor] = None):
-    """Causal grouped-query attention of every token of the step over its sequence's pages.  `softcap` > 0 caps the
+                      sink_values: Optional[torch.Tensor] = None, keep_first: int = 0):
+    """Causal grouped-query attention of every token of the step over its sequence's pages.  `keep_first` (with `window`):
+    the first so many keys of the sequence are seen beside the window's.  `softcap` > 0 caps the
     scores smoothly (s <- softcap * tanh(s / softcap)); `chunk`: a query reads only the keys of its own chunk of that
     many positions; `sink`: one more term exp(0), without a value, in the softmax's denominator (exp(sink_values[head])
     with `sink_values`, float32 [nq]); `value_dim`: the
@@ -433,14 +465,58 @@ def attention_generic(q, k_pages, v_pages, out, token_seq, token_pos, page_table
         raise KernelError("attention: a window or chunks, not both")
     fn = _fn("attention.cu", f"q3_attention_generic_{s}",
              [c_void_p] * 7 + [c_int, c_int64, c_int, c_int, c_int, c_float, c_int, c_int, c_float, c_int, c_int, c_int, c_int,
-                               c_void_p, c_void_p])
+                               c_void_p, c_int, c_void_p])
     _check(fn(_dev(q, "q"), _dev(k_pages, "k_pages", q.dtype), _dev(v_pages, "v_pages", q.dtype),
               _dev(out, "out"), _dev(token_seq, "token_seq", torch.int32),
               _dev(token_pos, "token_pos", torch.int32), _dev(page_table, "page_table", torch.int32),
               page_table.shape[-1], n_tokens, nq, nkv, d, float(scale), int(window or 0), vd, float(softcap or 0.0),
               int(chunk or 0), int(bool(sink)), nv, int(out.dtype == torch.float32 and q.dtype != torch.float32),
-              _sink_ptr(sink, sink_values, nq), _stream()),
+              _sink_ptr(sink, sink_values, nq), int(keep_first or 0) if window else 0, _stream()),
            "attention_generic")
+    return out
+
+
+def value_mix(rows: torch.Tensor, v_off: int, width: int, bias: Optional[torch.Tensor], first: torch.Tensor, save: bool,
+              lam: float = 0.0) -> torch.Tensor:
+    """On the columns [v_off, v_off + width) of every row, in place: v += bias (float32, may be None); then `save`:
+    first = v, a copy for later layers; else v = (1 - lam) v + lam first.  `first` [N, width] in the rows' type."""
+    N = rows.shape[0]
+    if first.shape != (N, width) or first.dtype != rows.dtype or (bias is not None and bias.numel() != width):
+        raise KernelError("value_mix: shapes do not fit")
+    fn = _fn("attention.cu", f"q3_value_mix_{_suffix(rows)}",
+             [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int, c_float, c_int64, c_void_p])
+    _check(fn(_dev(rows, "rows"), rows.shape[1], int(v_off), int(width), _ptr(bias, "bias", torch.float32), _dev(first, "first"),
+              int(bool(save)), float(lam), N, _stream()), "value_mix")
+    return rows
+
+
+def head_gate(x: torch.Tensor, gate: torch.Tensor, heads: int, vd: int) -> torch.Tensor:
+    """x[t, h, :] *= sigmoid(gate[t, h]) in place; x [N, heads * vd], `gate` a view of [N, heads] columns (its row
+    stride may be larger)."""
+    N = x.shape[0]
+    if x.shape[1] != heads * vd or gate.shape != (N, heads) or gate.stride(1) != 1 or gate.dtype != x.dtype or not x.is_contiguous():
+        raise KernelError("head_gate: shapes do not fit")
+    fn = _fn("attention.cu", f"q3_head_gate_{_suffix(x)}", [c_void_p, c_void_p, c_int64, c_int, c_int, c_int64, c_void_p])
+    _check(fn(x.data_ptr(), gate.data_ptr(), gate.stride(0), int(heads), int(vd), N, _stream()), "head_gate")
+    return x
+
+
+def short_conv(u: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, token_seq, seq_start, seq_slots, out: torch.Tensor,
+               n_seqs: int) -> torch.Tensor:
+    """Causal convolution over time on the first C columns of u [N, >= C]: out[t, c] = sum_j weight[c, j] u[t - taps + 1 + j, c]
+    within every sequence, the rows before the step from `state` (a view [slots, (taps - 1) * C] of float32 rows, the
+    oldest row first), which is moved on afterwards.  weight float32 [C, taps]; out [N, C] in u's type."""
+    N, (C, taps) = u.shape[0], weight.shape
+    if out.shape != (N, C) or out.dtype != u.dtype or u.shape[1] < C or u.stride(1) != 1 or state.shape[1] != (taps - 1) * C \
+            or state.dtype != torch.float32 or (taps > 1 and state.stride(1) != 1) or not out.is_contiguous() or out.data_ptr() == u.data_ptr():
+        raise KernelError("short_conv: shapes do not fit")
+    fn = _fn("short_conv.cu", f"q3_short_conv_{_suffix(u)}",
+             [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int, c_void_p])
+    _check(fn(u.data_ptr(), u.stride(0), _dev(weight, "weight", torch.float32), state.data_ptr(), state.stride(0),
+              _dev(token_seq, "token_seq", torch.int32), _dev(seq_start, "seq_start", torch.int32),
+              _dev(seq_slots, "seq_slots", torch.int32), out.data_ptr(), C, taps, N, int(n_seqs), _stream()), "short_conv")
+    if taps > 1:
+        _count_extra(1)
     return out
 
 
@@ -534,6 +610,80 @@ def gated_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: f
     return out
 
 
+# ------------------------------------------------------------------ linear attention with keys: a decay per channel, or gates per head
+def _scan_views(q, k, v, state, out, heads, d, vd, vdx):
+    row = q.stride(0)
+    if q.dtype != k.dtype or q.dtype != v.dtype or k.stride(0) != row or v.stride(0) != row or q.stride(1) != 1 or k.stride(1) != 1 \
+            or v.stride(1) != 1 or q.shape[1] != heads * d or k.shape[1] != heads * d or v.shape[1] != heads * vd \
+            or state.dtype != torch.float32 or state.shape[1] != heads * d * vdx or state.stride(1) != 1 \
+            or out.dtype != torch.float32 or out.shape[1] != heads * vdx or not out.is_contiguous():
+        raise KernelError("decay_scan: shapes do not fit")
+    return row
+
+
+def decay_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, seq_start: torch.Tensor, seq_slots: torch.Tensor,
+               out: torch.Tensor, n_seqs: int, heads: int, d: int, vd: int, q_scale: float = 1.0, z: Optional[torch.Tensor] = None,
+               z_bias: Optional[torch.Tensor] = None, tau: float = 1.0, keep: Optional[torch.Tensor] = None,
+               write: Optional[torch.Tensor] = None, ones: bool = False) -> torch.Tensor:
+    """S_t = diag(a_t) S_(t-1) + k_t (b_t v_t)^T, o_t = S_t^T (q_t * q_scale) over the new tokens of every sequence, from and to
+    the state rows (`state`: a view [slots, heads * d * vdx] of float32 rows).  q, k, v: column views of one projection
+    output (same row stride).  With `z` [N, heads * d] (float32 logits): a = sigmoid(z + z_bias)^(1 / tau) per channel,
+    b = 1.  With `keep`, `write` [N, heads] (float32): a and b per head.  `ones`: vdx = vd + 1, the state's last column takes
+    the value 1 (a normaliser); else vdx = vd.  out [N, heads * vdx] float32."""
+    vdx = vd + (1 if ones else 0)
+    row = _scan_views(q, k, v, state, out, heads, d, vd, vdx)
+    N = q.shape[0]
+    if (z is None) == (keep is None) or (z is not None and (tuple(z.shape) != (N, heads * d) or not z.is_contiguous())) \
+            or (keep is not None and (write is None or keep.numel() < N * heads or write.numel() < N * heads)):
+        raise KernelError("decay_scan: a decay per channel (z) or gates per head (keep, write)")
+    fn = _fn("linear_scan.cu", f"q3_decay_scan_{_suffix(q)}",
+             [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_float, c_int, c_void_p, c_int64,
+              c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), row, _ptr(z, "z", torch.float32), _ptr(z_bias, "z_bias", torch.float32),
+              1.0 / float(tau), _ptr(keep, "keep", torch.float32), _ptr(write, "write", torch.float32), float(q_scale), int(bool(ones)),
+              state.data_ptr(), state.stride(0), _dev(seq_start, "seq_start", torch.int32), _dev(seq_slots, "seq_slots", torch.int32),
+              _dev(out, "out"), int(n_seqs), heads, d, vd, _stream()), "decay_scan")
+    return out
+
+
+def memory_gates(z: torch.Tensor, bias_i: torch.Tensor, bias_f: torch.Tensor, cap: float, m_state: torch.Tensor, seq_start, seq_slots,
+                 keep: torch.Tensor, write: torch.Tensor, low: torch.Tensor, n_seqs: int, heads: int) -> None:
+    """The gates of a matrix memory from z [N, 2 heads] (float32: input-gate logits, then forget-gate logits):
+    i = cap tanh((zi + bias_i) / cap), f = logsigmoid(cap tanh((zf + bias_f) / cap)), the running maximum
+    m_t = max(f_t + m_(t-1), i_t) from and to `m_state` (a view [slots, heads]), keep = exp(f + m_(t-1) - m_t),
+    write = exp(i - m_t), low = exp(-m_t); all [N, heads] float32."""
+    N = z.shape[0]
+    if z.shape[1] != 2 * heads or z.dtype != torch.float32 or not z.is_contiguous() or m_state.shape[1] != heads \
+            or m_state.stride(1) != 1 or m_state.dtype != torch.float32 or min(keep.numel(), write.numel(), low.numel()) < N * heads:
+        raise KernelError("memory_gates: shapes do not fit")
+    fn = _fn("linear_scan.cu", "q3_memory_gates",
+             [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+              c_int64, c_int, c_void_p])
+    _check(fn(z.data_ptr(), z.data_ptr() + 4 * heads, _dev(bias_i, "bias_i", torch.float32), _dev(bias_f, "bias_f", torch.float32),
+              float(cap), m_state.data_ptr(), m_state.stride(0), _dev(seq_start, "seq_start", torch.int32),
+              _dev(seq_slots, "seq_slots", torch.int32), _dev(keep, "keep", torch.float32), _dev(write, "write", torch.float32),
+              _dev(low, "low", torch.float32), heads, 2 * heads, int(n_seqs), _stream()), "memory_gates")
+
+
+def head_gated_norm(o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, eps: float, out: torch.Tensor, heads: int, vd: int,
+                    act: str = "sigmoid", low: Optional[torch.Tensor] = None, floor: float = 0.0) -> torch.Tensor:
+    """Per (token, head): x = o[t, h, :vd] (with `low` [N, heads]: divided by max(|o[t, h, vd]|, low) + floor, the row then
+    holding vd + 1 values), out = x / sqrt(mean(x^2) + eps) * weight * act(gate), act 'sigmoid' or 'silu'; `weight` float32
+    [vd] (one for all heads) or [heads * vd]; `gate` a view of [N, heads * vd] columns; out in the gate's type."""
+    N = o.shape[0]
+    vdx = vd + (1 if low is not None else 0)
+    if o.shape[1] != heads * vdx or o.dtype != torch.float32 or not o.is_contiguous() or weight.numel() not in (vd, heads * vd) \
+            or gate.shape != (N, heads * vd) or gate.stride(1) != 1 or out.shape != (N, heads * vd) or out.dtype != gate.dtype \
+            or not out.is_contiguous() or act not in ("sigmoid", "silu") or (low is not None and low.numel() < N * heads):
+        raise KernelError("head_gated_norm: shapes do not fit")
+    fn = _fn("linear_scan.cu", f"q3_head_gated_norm_{_suffix(out)}",
+             [c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    _check(fn(o.data_ptr(), _ptr(low, "low", torch.float32), float(floor), _dev(weight, "weight", torch.float32),
+              int(weight.numel() == heads * vd and heads > 1), gate.data_ptr(), gate.stride(0), out.data_ptr(), N, heads, vd, vdx, float(eps),
+              int(act == "silu"), _stream()), "head_gated_norm")
+    return out
+
+
 # ------------------------------------------------------------------ differential attention
 def diff_combine(a: torch.Tensor, out: torch.Tensor, n_tokens: int, heads: int, per_group: int, vd: int, lam: float, eps: float,
                  gain: float) -> torch.Tensor:
@@ -562,23 +712,25 @@ def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> torch.Tensor:
 
 def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, top_ids: torch.Tensor, top_w: torch.Tensor,
               id_weight: torch.Tensor, n_real: int, top: int, group_count: int = 1, group_keep: int = 1, by_logit: bool = False,
-              gate_out: Optional[torch.Tensor] = None) -> None:
-    """Router of a mixture of experts for every token of h [N, hidden]: float32 logits, softmax over all outputs,
-    choice by score + correction within the kept groups, weights = plain scores; `by_logit`: the largest logits are
-    chosen and weighted by the softmax over the chosen logits alone (the correction is not read).  With `gate_out`
-    [N] the router matrix has one more row, and gate_out = sigmoid of its logit; see csrc/moe.cu."""
+              gate_out: Optional[torch.Tensor] = None, sigmoid: bool = False, group_pair: bool = False,
+              weight_scale: float = 1.0) -> None:
+    """Router of a mixture of experts for every token of h [N, hidden]: float32 logits, softmax over all outputs
+    (`sigmoid`: each output's sigmoid by itself), choice by score + correction within the kept groups (a group's mark:
+    its best choice score, or with `group_pair` the sum of its two best), weights = plain scores times `weight_scale`;
+    `by_logit`: the largest logits are chosen and weighted by the softmax over the chosen logits alone (the correction is
+    not read).  With `gate_out` [N] the router matrix has one more row, and gate_out = sigmoid of its logit; see csrc/moe.cu."""
     N, hidden = h.shape
     n_out = w_router.shape[0] - (1 if gate_out is not None else 0)
     if w_router.shape[1] != hidden or w_router.dtype != h.dtype or (correction is not None and correction.numel() != n_out) \
             or (correction is None and not by_logit) or top_ids.numel() < N * top or top_w.numel() < N * top or id_weight.numel() < N \
-            or (gate_out is not None and gate_out.numel() < N):
+            or (gate_out is not None and gate_out.numel() < N) or (by_logit and sigmoid):
         raise KernelError("moe_route: shapes do not fit")
     fn = _fn("moe.cu", f"q3_moe_route_{_suffix(h)}",
-             [c_void_p] * 6 + [c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+             [c_void_p] * 6 + [c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_float, c_void_p])
     _check(fn(_dev(h, "h"), _dev(w_router, "w_router"), _ptr(correction, "correction", torch.float32),
               _dev(top_ids, "top_ids", torch.int32), _dev(top_w, "top_w", torch.float32), _dev(id_weight, "id_weight", torch.float32),
-              N, hidden, n_out, int(n_real), int(top), int(group_count), int(group_keep), int(bool(by_logit)),
-              _ptr(gate_out, "gate_out", torch.float32), _stream()), "moe_route")
+              N, hidden, n_out, int(n_real), int(top), int(group_count), int(group_keep), 1 if by_logit else (2 if sigmoid else 0),
+              _ptr(gate_out, "gate_out", torch.float32), int(bool(group_pair)), float(weight_scale), _stream()), "moe_route")
 
 
 def moe_sort(top_ids: torch.Tensor, n_pairs: int, n_real: int, offsets: torch.Tensor, slot_of_pair: torch.Tensor,

@@ -1,0 +1,81 @@
+// A short causal convolution over time on every channel of a projection's rows, with the last taps - 1 input rows of
+// every sequence kept as its state:
+//
+//     y[t, c] = sum_j w[c, j] * u[t - taps + 1 + j, c],   j = 0 .. taps - 1,   u = 0 before the sequence's start
+//
+//   short_conv       : one thread per (token, channel); an input row before the step's first token comes from the
+//                      state [slot][taps - 1][C] (float32; the oldest row first), which holds zeros for a new sequence.
+//                      The products are summed in 32-bit in ascending j whatever the step, so a token's output is the
+//                      same bits however the sequence was cut.
+//   short_conv_state : afterwards, one thread per (sequence, channel) moves the state on: the last taps - 1 rows of
+//                      (old state, the step's rows).
+//
+// u has `row_in` values per row (the convolved channels are its first C), y is dense [N, C]; w float32 [C, taps].
+#include "common.cuh"
+
+namespace {
+
+template <typename T>
+__global__ void short_conv_kernel(const T* __restrict__ u, int64_t row_in, const float* __restrict__ w, const float* __restrict__ state,
+                                  int64_t slot_stride, const int* __restrict__ token_seq, const int* __restrict__ seq_start,
+                                  const int* __restrict__ seq_slots, T* __restrict__ y, int C, int taps, int64_t n_tokens) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t total = n_tokens * C;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = i / C;
+        const int c = (int)(i % C);
+        const int seq = token_seq[t];
+        const int64_t first = seq_start[seq];                  // the step's first row of this sequence
+        const float* st = state + (int64_t)seq_slots[seq] * slot_stride;
+        float acc = 0.0f;
+        for (int j = 0; j < taps; ++j) {
+            const int64_t src = t - (taps - 1) + j;
+            const float x = src >= first ? to_f32<T>(u[src * row_in + c]) : st[(int64_t)(taps - 1 + (src - first)) * C + c];
+            acc = fmaf(w[(int64_t)c * taps + j], x, acc);
+        }
+        y[i] = from_f32<T>(acc);
+    }
+}
+
+template <typename T>
+__global__ void short_conv_state_kernel(const T* __restrict__ u, int64_t row_in, float* __restrict__ state, int64_t slot_stride,
+                                        const int* __restrict__ seq_start, const int* __restrict__ seq_slots, int C, int taps,
+                                        int n_seqs) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t total = (int64_t)n_seqs * C;
+    const int keep = taps - 1;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int seq = (int)(i / C), c = (int)(i % C);
+        const int64_t first = seq_start[seq], n_new = seq_start[seq + 1] - first;
+        float* st = state + (int64_t)seq_slots[seq] * slot_stride;
+        // row r of the new state is row r + n_new of (old state, new rows): ascending r never reads what it wrote
+        for (int r = 0; r < keep; ++r) {
+            const int64_t src = r + n_new;
+            st[(int64_t)r * C + c] = src < keep ? st[src * C + c] : to_f32<T>(u[(first + src - keep) * row_in + c]);
+        }
+    }
+}
+
+}  // namespace
+
+#define Q3_CONV_EXPORTS(SUFFIX, T)                                                                                        \
+    Q3_EXPORT int q3_short_conv_##SUFFIX(const void* u, int64_t row_in, const float* w, float* state, int64_t slot_stride, \
+                                         const int* token_seq, const int* seq_start, const int* seq_slots, void* y,      \
+                                         int channels, int taps, int64_t n_tokens, int n_seqs, void* stream) {           \
+        if (n_tokens <= 0 || n_seqs <= 0) return 0;                                                                       \
+        if (channels <= 0 || taps <= 0 || taps > 64 || row_in < channels) return Q3_ERR_BAD_SIZE;                         \
+        const int64_t blocks = (n_tokens * channels + 255) / 256;                                                         \
+        int code = (int)q3_launch(short_conv_kernel<T>, dim3((unsigned)(blocks < 65536 ? blocks : 65536)), dim3(256), 0,  \
+                                  (cudaStream_t)stream, (const T*)u, row_in, w, (const float*)state, slot_stride,         \
+                                  token_seq, seq_start, seq_slots, (T*)y, channels, taps, n_tokens);                      \
+        if (code != 0 || taps == 1) return code;                                                                          \
+        const int64_t sblocks = ((int64_t)n_seqs * channels + 255) / 256;                                                 \
+        return (int)q3_launch(short_conv_state_kernel<T>, dim3((unsigned)(sblocks < 65536 ? sblocks : 65536)), dim3(256), \
+                              0, (cudaStream_t)stream, (const T*)u, row_in, state, slot_stride, seq_start, seq_slots,     \
+                              channels, taps, n_seqs);                                                                    \
+    }
+
+Q3_CONV_EXPORTS(f32, float)
+Q3_CONV_EXPORTS(bf16, bf16)

@@ -26,4 +26,6 @@ def all_variants():
         ("stream_shift.cu", ()),
         ("gated_recurrence.cu", ()),
         ("latent.cu", ()),
+        ("linear_scan.cu", ()),
+        ("short_conv.cu", ()),
     ]

@@ -6,7 +6,7 @@
 // values live in *pages* of `page_tokens` tokens; a slot holds, for every layer group, a list of
 // pages that covers its length.  Layers whose mixers ask the same of the cache form a *group* with
 // a page pool of its own; a group that needs only a window of keys returns the pages that fell out
-// of the window after each step, and a group whose queries read only the keys of their own chunk of
+// of the window after each step (but for the pages of the first keys, if its queries keep reading those), and a group whose queries read only the keys of their own chunk of
 // positions (chunks of a fixed size, counted from position 0) returns the pages of finished chunks.
 //
 // A step is three calls: reserve (all or nothing: a step that does not fit changes nothing), the
@@ -40,8 +40,8 @@ enum class GroupKind : int { Full = 0, Window = 1, Chunk = 2 };
 // The pages of the layers that share one need.
 class PageGroup {
 public:
-    PageGroup(GroupKind kind, int window, int n_pages, int n_slots, int pages_per_slot, int page_tokens)
-        : kind_(kind), window_(window), n_pages_(n_pages), pages_per_slot_(pages_per_slot), page_tokens_(page_tokens),
+    PageGroup(GroupKind kind, int window, int n_pages, int n_slots, int pages_per_slot, int page_tokens, int keep_first = 0)
+        : kind_(kind), window_(window), keep_first_(keep_first), n_pages_(n_pages), pages_per_slot_(pages_per_slot), page_tokens_(page_tokens),
           table_((size_t)n_slots * pages_per_slot, -1), first_live_(n_slots, 0) {
         free_.reserve(n_pages);
         for (int p = n_pages - 1; p >= 0; --p) free_.push_back(p);
@@ -89,7 +89,9 @@ public:
             dead = (length / window_ * window_) / page_tokens_;
         }
         int32_t* r = table_.data() + (size_t)slot * pages_per_slot_;
-        for (int64_t i = first_live_[slot]; i < dead; ++i)
+        // the pages that hold one of the first `keep_first` keys stay: every later query of a window group reads them
+        const int64_t kept = kind_ == GroupKind::Window ? pages_for(keep_first_) : 0;
+        for (int64_t i = std::max(first_live_[slot], kept); i < dead; ++i)
             if (r[i] >= 0) {
                 free_.push_back(r[i]);
                 r[i] = -1;
@@ -110,7 +112,7 @@ private:
     int64_t pages_for(int64_t tokens) const { return (tokens + page_tokens_ - 1) / page_tokens_; }
 
     GroupKind kind_;
-    int window_, n_pages_, pages_per_slot_, page_tokens_;
+    int window_, keep_first_, n_pages_, pages_per_slot_, page_tokens_;
     std::vector<int32_t> free_, table_;
     std::vector<int64_t> first_live_;
 };
@@ -119,6 +121,7 @@ private:
 struct GroupNeed {
     GroupKind kind = GroupKind::Full;
     int window = 0;        // Window groups: the number of keys a query reads; Chunk groups: the size of a chunk
+    int keep_first = 0;    // Window groups: so many keys at the start of a sequence stay readable beside the window
 };
 
 class CacheBook {
@@ -137,7 +140,8 @@ public:
         for (int s = n_slots_ - 1; s >= 0; --s) free_slots_.push_back(s);
         for (const GroupNeed& g : groups) {
             if (g.kind != GroupKind::Full && g.window <= 0) throw std::invalid_argument("a window or chunk group needs a positive size");
-            groups_.emplace_back(g.kind, g.window, n_pages_, n_slots_, pages_per_slot_, page_tokens);
+            if (g.keep_first < 0) throw std::invalid_argument("keep_first must not be negative");
+            groups_.emplace_back(g.kind, g.window, n_pages_, n_slots_, pages_per_slot_, page_tokens, g.keep_first);
         }
     }
 

@@ -93,15 +93,15 @@ int q3_qkv_prepare_bf16(const void* qkv, void* q_out, void* k_pages, void* v_pag
    value_heads 0 = nkv, else each value head serves nkv / value_heads key heads; out_f32: `out` is float whatever q is;
    softcap > 0: scores s <- softcap * tanh(s / softcap); chunk > 0: a query reads the keys of its own chunk of that many
    positions only; sink != 0: one more term exp(0) in the softmax's denominator, or exp(sink_values[head]) where sink_values
-   (one float per query head) is given */
+   (one float per query head) is given; keep_first (with window): the first so many keys of the sequence are seen too */
 int q3_attention_generic_f32(const void* q, const void* k_pages, const void* v_pages, void* out, const int* token_seq,
                              const int* token_pos, const int* page_table, int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d,
                              float scale, int window, int value_dim, float softcap, int chunk, int sink, int value_heads, int out_f32,
-                             const float* sink_values, void* stream);
+                             const float* sink_values, int keep_first, void* stream);
 int q3_attention_generic_bf16(const void* q, const void* k_pages, const void* v_pages, void* out, const int* token_seq,
                               const int* token_pos, const int* page_table, int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d,
                               float scale, int window, int value_dim, float softcap, int chunk, int sink, int value_heads, int out_f32,
-                              const float* sink_values, void* stream);
+                              const float* sink_values, int keep_first, void* stream);
 
 /* the same from the q/k/v projection's output as it is: bias (may be null), rotation of the first rotary_dim values of q and k
    (tables may be null) and the write of the new key and value into their pages in the attention's own kernel */
@@ -236,13 +236,14 @@ int q3_diff_combine_bf16(const float* a, void* out, int64_t n_tokens, int heads,
 /* per token: float32 router logits, softmax, choice by score + correction within the kept groups, weights = scores;
    the outputs from n_real on are identity experts (their weights are summed into id_weight); by_logit: the largest logits
    are chosen, weighted by the softmax over the chosen logits alone; gate_out (may be null): the router matrix has one more
-   row and gate_out[t] = sigmoid of its logit */
+   row and gate_out[t] = sigmoid of its logit; by_logit 2: scores sigmoid(z) instead of the softmax; group_pair: a group's mark
+   is the sum of its two best choice scores; the weights are multiplied by weight_scale */
 int q3_moe_route_f32(const void* h, const void* w_router, const float* correction, int* top_ids, float* top_w, float* id_weight,
                      int64_t n_tokens, int hidden, int n_out, int n_real, int top, int group_count, int group_keep, int by_logit,
-                      float* gate_out, void* stream);
+                     float* gate_out, int group_pair, float weight_scale, void* stream);
 int q3_moe_route_bf16(const void* h, const void* w_router, const float* correction, int* top_ids, float* top_w, float* id_weight,
                       int64_t n_tokens, int hidden, int n_out, int n_real, int top, int group_count, int group_keep, int by_logit,
-                      float* gate_out, void* stream);
+                      float* gate_out, int group_pair, float weight_scale, void* stream);
 /* offsets [n_real + 1], slot_of_pair (-1: identity) and pair_of_slot of the (token, choice) pairs laid out by expert */
 int q3_moe_sort(const int* top_ids, int n_pairs, int n_real, int* offsets, int* slot_of_pair, int* pair_of_slot, void* stream);
 /* act[slot] = g sigmoid(alpha g) (u + up_offset), g = min(W_gate x, limit), u = clamp(W_up x, -limit, limit); y[slot] = W_down act */
@@ -316,6 +317,57 @@ int q3_head_product_f32(const void* x, int64_t x_row, int x_head, int x_off, con
                         int out_off, const void* gate, int64_t gate_row, int64_t n_tokens, int heads, int K, int N, void* stream);
 int q3_head_product_bf16(const void* x, int64_t x_row, int x_head, int x_off, const void* w, void* out, int64_t out_row, int out_head,
                          int out_off, const void* gate, int64_t gate_row, int64_t n_tokens, int heads, int K, int N, void* stream);
+
+/* ---- elementwise.cu: the clamped gated activation, a weighted sum, a bias ------------------------------------ */
+/* out = g sigmoid(alpha g) (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit); the layout of q3_act_mul */
+int q3_clamped_mul_f32(const void* gate_up, void* out, int64_t rows, int inter, int interleaved, float limit, float alpha, void* stream);
+int q3_clamped_mul_bf16(const void* gate_up, void* out, int64_t rows, int inter, int interleaved, float limit, float alpha, void* stream);
+/* out = sa * a + sb * b */
+int q3_scaled_sum_f32(const void* a, const void* b, float sa, float sb, void* out, int64_t n, void* stream);
+int q3_scaled_sum_bf16(const void* a, const void* b, float sa, float sb, void* out, int64_t n, void* stream);
+/* x[r, c] += bias[c] */
+int q3_add_bias_f32(void* x, const float* bias, int64_t rows, int size, void* stream);
+int q3_add_bias_bf16(void* x, const float* bias, int64_t rows, int size, void* stream);
+
+/* ---- attention.cu: values blended across layers, a gate per head --------------------------------------------- */
+/* on columns [v_off, v_off + width) of rows of `row` values: v += bias; save: first = v; else v = (1 - lambda) v + lambda first */
+int q3_value_mix_f32(void* rows, int64_t row, int64_t v_off, int width, const float* bias, void* first, int save, float lambda,
+                     int64_t n_tokens, void* stream);
+int q3_value_mix_bf16(void* rows, int64_t row, int64_t v_off, int width, const float* bias, void* first, int save, float lambda,
+                      int64_t n_tokens, void* stream);
+/* x[t, h, :] *= sigmoid(gate[t, h]) */
+int q3_head_gate_f32(void* x, const void* gate, int64_t gate_row, int heads, int vd, int64_t n_tokens, void* stream);
+int q3_head_gate_bf16(void* x, const void* gate, int64_t gate_row, int heads, int vd, int64_t n_tokens, void* stream);
+
+/* ---- short_conv.cu ------------------------------------------------------------------------------------------- */
+/* y[t, c] = sum_j w[c, j] u[t - taps + 1 + j, c] within every sequence; rows before the step come from state
+   [slot][taps - 1][channels] (float32), which is moved on afterwards */
+int q3_short_conv_f32(const void* u, int64_t row_in, const float* w, float* state, int64_t slot_stride, const int* token_seq,
+                      const int* seq_start, const int* seq_slots, void* y, int channels, int taps, int64_t n_tokens, int n_seqs,
+                      void* stream);
+int q3_short_conv_bf16(const void* u, int64_t row_in, const float* w, float* state, int64_t slot_stride, const int* token_seq,
+                       const int* seq_start, const int* seq_slots, void* y, int channels, int taps, int64_t n_tokens, int n_seqs,
+                       void* stream);
+
+/* ---- linear_scan.cu: linear attention with keys ------------------------------------------------------------- */
+/* S_t = diag(a_t) S_(t-1) + k_t (b_t v_t)^T, o_t = S_t^T (q_t q_scale); z given: a = sigmoid(z + z_bias)^inv_tau per channel,
+   b = 1; keep and write given: a and b per (token, head); ones: the state has a last column whose value is 1 */
+int q3_decay_scan_f32(const void* q, const void* k, const void* v, int64_t row, const float* z, const float* z_bias, float inv_tau,
+                      const float* keep, const float* write, float q_scale, int ones, float* state, int64_t slot_stride,
+                      const int* seq_start, const int* seq_slots, float* out, int n_seqs, int heads, int d, int vd, void* stream);
+int q3_decay_scan_bf16(const void* q, const void* k, const void* v, int64_t row, const float* z, const float* z_bias, float inv_tau,
+                       const float* keep, const float* write, float q_scale, int ones, float* state, int64_t slot_stride,
+                       const int* seq_start, const int* seq_slots, float* out, int n_seqs, int heads, int d, int vd, void* stream);
+/* i = cap tanh((zi + bias_i) / cap), f = logsigmoid(cap tanh((zf + bias_f) / cap)), m_t = max(f_t + m_(t-1), i_t) from and to
+   m_state; keep = exp(f + m_(t-1) - m_t), write = exp(i - m_t), low = exp(-m_t) */
+int q3_memory_gates(const float* zi, const float* zf, const float* bias_i, const float* bias_f, float cap, float* m_state,
+                    int64_t slot_stride, const int* seq_start, const int* seq_slots, float* keep, float* write, float* low, int heads,
+                    int64_t z_row, int n_seqs, void* stream);
+/* per (token, head): x = o[:vd] (/ (max(|o[vd]|, low) + floor_add) if vdx > vd); out = x / sqrt(mean(x^2) + eps) * w * act(gate) */
+int q3_head_gated_norm_f32(const float* o, const float* low, float floor_add, const float* w, int w_per_head, const void* gate,
+                           int64_t gate_row, void* out, int64_t n_tokens, int heads, int vd, int vdx, float eps, int act, void* stream);
+int q3_head_gated_norm_bf16(const float* o, const float* low, float floor_add, const float* w, int w_per_head, const void* gate,
+                            int64_t gate_row, void* out, int64_t n_tokens, int heads, int vd, int vdx, float eps, int act, void* stream);
 
 /* ---- sampling.cu ------------------------------------------------------------------------------------------ */
 /* out[r] = index of the highest logit among the first `valid` (lowest id among equals, NaN as -inf) */

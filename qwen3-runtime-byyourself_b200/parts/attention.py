@@ -15,6 +15,15 @@ chunks counted from position 0 of the sequence), a sink (`sink`: the softmax's d
 one more term exp(0), which carries no value), an interleaved rotary encoding (the rows of the
 q and k projections are reordered at load time so that the kernels' half-split rotation
 applies), and the checkpoint names of the tensors (`names`).
+
+Further still, for other designs: `keep_first` (with `window`): every query also sees the first so many keys of its
+sequence, at their true positions; `out_bias`: a bias on the output projection; `conv_taps`: a short causal convolution
+over time on every channel of q, k and v right after the projection, before the rotation (tensors `<q|k|v>` +
+`conv_suffix`, [channels, taps]; the last taps - 1 projected rows of a sequence are part of its state);
+`head_gate`: every head's output is multiplied by sigmoid(w_h . x), one number per token and head (tensor `head_gate`
+[heads, hidden]); `value_mix`: values blended across layers: the layer that says "first" keeps the step's values
+(after the bias) for the others, a layer that says "blend" goes on with v <- (1 - lambda) v + lambda v_first, lambda
+its scalar tensor `value_mix`, and caches the blend (a "first" layer may store the scalar too; it is not read).
 """
 from __future__ import annotations
 
@@ -43,7 +52,8 @@ FUSED_PROJECTION_KERNELS = []
 
 TENSOR_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
                 "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
-                "q_norm": "q_norm.weight", "k_norm": "k_norm.weight"}
+                "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "o_bias": "o_proj.bias", "value_mix": "value_mix",
+                "head_gate": "gate.weight", "conv_suffix": ".conv"}
 
 
 class GQAAttention(Part):
@@ -51,7 +61,9 @@ class GQAAttention(Part):
                  qk_norm: Optional[PartSpec] = None, position: Optional[PartSpec] = None,
                  window: Optional[int] = None, prefix: str = "", value_dim: Optional[int] = None, bias: bool = False,
                  softcap: Optional[float] = None, chunk: Optional[int] = None, sink: bool = False,
-                 names: Optional[dict] = None, value_heads: Optional[int] = None, out_float32: bool = False):
+                 names: Optional[dict] = None, value_heads: Optional[int] = None, out_float32: bool = False,
+                 keep_first: int = 0, out_bias: bool = False, value_mix: Optional[str] = None, conv_taps: int = 0,
+                 head_gate: bool = False):
         self.sink_values = None      # float32 [num_heads]: the sink's score per head, for a part that has learned ones (else 0)
         if num_heads % num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
@@ -61,6 +73,13 @@ class GQAAttention(Part):
                              f"(the tensor-core kernels: multiples of 16)")
         if window and chunk:
             raise ValueError("attention takes a window or chunks, not both")
+        if value_mix not in (None, "first", "blend") or keep_first < 0 or conv_taps < 0 or (keep_first and not window):
+            raise ValueError("attention: value_mix is 'first' or 'blend'; keep_first goes with a window")
+        self.keep_first, self.out_bias, self.value_mix = int(keep_first), bool(out_bias), value_mix
+        self.conv_taps, self.head_gate = int(conv_taps), bool(head_gate)
+        self.out_name = "mixer.out"  # the scratch buffer of the result; a part that runs several mixers side by side renames it
+        self.o_bias = self.bias_v = self.conv_weight = self.w_gate = None
+        self.mix_lambda = 0.0
         self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = hidden_size, num_heads, num_kv_heads, head_dim
         self.scale, self.window, self.prefix = float(scale), window, prefix
         self.value_dim, self.has_bias, self.sink = value_dim, bool(bias), bool(sink)
@@ -81,7 +100,7 @@ class GQAAttention(Part):
         self.reordered = False       # the rows of the q and k projections follow the position encoding's kernel order
         # what the kernels written for Qwen3's attention take
         self.plain = not (self.has_bias or self.softcap or self.chunk or self.sink or value_dim != head_dim or head_dim % 16
-                          or self.shared_values)
+                          or self.shared_values or self.keep_first or self.value_mix)
 
     # -- weights
     def weight_specs(self, prefix: str) -> dict:
@@ -95,6 +114,15 @@ class GQAAttention(Part):
         if self.q_norm is not None:
             specs.update(self.q_norm.weight_specs(p + n["q_norm"]))
             specs.update(self.k_norm.weight_specs(p + n["k_norm"]))
+        if self.out_bias:
+            specs[p + n["o_bias"]] = WeightSpec((H,), "bias")
+        if self.value_mix:
+            specs[p + n["value_mix"]] = WeightSpec((), "bias")
+        if self.head_gate:
+            specs[p + n["head_gate"]] = WeightSpec((nq, H))
+        if self.conv_taps:
+            for which, rows in (("q", nq * d), ("k", nkv * d), ("v", nv * vd)):
+                specs[p + n[which] + n["conv_suffix"]] = WeightSpec((rows, self.conv_taps), "bias")
         return specs
 
     def output_width(self) -> int:
@@ -110,6 +138,23 @@ class GQAAttention(Part):
             tensors = [weights[p + n[k]] for k in ("q_bias", "k_bias", "v_bias")]
             getattr(weights, "wait", lambda: None)()          # a streamed checkpoint: the tensors are in place now
             self.bias = torch.cat([t.to(device=device, dtype=torch.float32).reshape(-1) for t in tensors]).contiguous()
+        f32 = dict(device=device, dtype=torch.float32)
+        if self.out_bias:
+            self.o_bias = weights[p + n["o_bias"]].to(**f32).contiguous()
+        if self.head_gate:
+            self.w_gate = weights.pop(p + n["head_gate"]).contiguous()
+        if self.conv_taps:
+            taps = [weights[p + n[which] + n["conv_suffix"]] for which in ("q", "k", "v")]
+            getattr(weights, "wait", lambda: None)()
+            self.conv_weight = torch.cat([t.to(**f32) for t in taps], dim=0).contiguous()
+        if self.value_mix:
+            lam = weights[p + n["value_mix"]]
+            getattr(weights, "wait", lambda: None)()
+            self.mix_lambda = float(lam.to(torch.float32).reshape(-1)[0].item()) if self.value_mix == "blend" else 0.0
+            if self.bias is not None:          # the values' bias is added where they are blended, before the cache write
+                v0 = (nq + nkv) * d
+                self.bias_v = self.bias[v0:].clone()
+                self.bias[v0:] = 0.0
         order = self.position.kernel_order() if self.position is not None and hasattr(self.position, "kernel_order") else None
         if order is not None:
             # q.k does not change when the values of every query and key head are reordered alike: put the pairs
@@ -122,6 +167,8 @@ class GQAAttention(Part):
             self.w_qkv[:rows.numel()] = self.w_qkv[:rows.numel()][rows]
             if self.bias is not None:
                 self.bias[:rows.numel()] = self.bias[:rows.numel()][rows]
+            if self.conv_weight is not None:
+                self.conv_weight[:rows.numel()] = self.conv_weight[:rows.numel()][rows]
             self.reordered = True
         if self.q_norm is not None:
             self.q_norm.bind(weights, p + n["q_norm"], dtype, device)
@@ -130,14 +177,25 @@ class GQAAttention(Part):
     # -- cache
     def cache_need(self) -> CacheNeed:
         kind = "window" if self.window else ("chunk" if self.chunk else "full")
+        state = ((self.conv_taps - 1) * self.projection_width(),) if self.conv_taps > 1 else ()
         return CacheNeed(kind, self.num_kv_heads, self.head_dim, self.window or self.chunk,
                          value_dim=self.value_dim if self.value_dim != self.head_dim else None,
-                         value_heads=self.value_heads if self.value_heads != self.num_kv_heads else None)
+                         value_heads=self.value_heads if self.value_heads != self.num_kv_heads else None,
+                         keep_first=self.keep_first if self.window else 0, state_shape=state)
+
+    def projection_width(self) -> int:
+        """Columns of the q/k/v projection."""
+        return (self.num_heads + self.num_kv_heads) * self.head_dim + self.value_heads * self.value_dim
 
     # -- step
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
-        out = ctx.scratch.get("mixer.out", (ctx.n_tokens, self.hidden_size), ctx.dtype)
-        return linear(self.mix(x, ctx, cache), self.w_o, out)
+        out = ctx.scratch.get(self.out_name, (ctx.n_tokens, self.hidden_size), ctx.dtype)
+        attn = self.mix(x, ctx, cache)
+        if self.head_gate:
+            gate = ctx.scratch.get("attn.head_gate", (ctx.n_tokens, self.num_heads), ctx.dtype)
+            ops.head_gate(attn, linear(x, self.w_gate, gate), self.num_heads, self.value_dim)
+        linear(attn, self.w_o, out)
+        return ops.add_bias(out, self.o_bias) if self.out_bias else out
 
     def mix(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
         """Everything before the output projection: [N, num_heads * value_dim] in the compute type (float32 with
@@ -155,14 +213,26 @@ class GQAAttention(Part):
             self.position.prepare(ctx.max_positions, ctx.device)
             cos, sin = self.position.cos, self.position.sin
         special = ctx.dtype == torch.bfloat16
-        if tables and not ctx.is_decode and special:
+        if tables and not ctx.is_decode and special and not self.conv_taps and not self.value_mix:
             q = ctx.scratch.get("attn.q", (N, nq * d), ctx.dtype)
             for kernel in FUSED_PROJECTION_KERNELS:
                 if kernel(self, x, cache, q, ctx, table, qw, kw, norm_eps, cos, sin):
                     self.attend(q, cache, attn, ctx, table)
                     return attn
-        qkv = ctx.scratch.get("attn.qkv", (N, (nq + nkv) * d + self.value_heads * vd), ctx.dtype)
-        linear(x, self.w_qkv, qkv)
+        qkv = ctx.scratch.get("attn.qkv", (N, self.projection_width()), ctx.dtype)
+        if self.conv_taps:
+            raw = ctx.scratch.get("attn.qkv_raw", (N, self.projection_width()), ctx.dtype)
+            linear(x, self.w_qkv, raw)
+            if self.conv_taps > 1 and cache.state is None:
+                raise ops.KernelError("the short convolution keeps rows per sequence: the cache was built without its state")
+            state = cache.state.view(cache.state.shape[0], -1) if cache.state is not None else raw.new_zeros((1, 0), dtype=torch.float32)
+            ops.short_conv(raw, self.conv_weight, state, ctx.token_seq, ctx.seq_start, ctx.seq_slots, qkv, ctx.n_seqs)
+        else:
+            linear(x, self.w_qkv, qkv)
+        if self.value_mix:
+            width = self.value_heads * vd
+            first = ctx.scratch.get("attn.v_first", (N, width), ctx.dtype)      # one buffer for the step: layers run in order
+            ops.value_mix(qkv, (nq + nkv) * d, width, self.bias_v, first, self.value_mix == "first", self.mix_lambda)
         if tables and ctx.is_decode and special:
             for kernel in FUSED_DECODE_KERNELS:
                 if kernel(self, qkv, cache, attn, ctx, table, qw, kw, norm_eps, cos, sin):
@@ -185,7 +255,7 @@ class GQAAttention(Part):
         ops.attention_generic(q, cache.keys, cache.values, out, ctx.token_seq, ctx.token_pos, table, ctx.n_tokens,
                               self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.window,
                               value_dim=self.value_dim, softcap=self.softcap, chunk=self.chunk, sink=self.sink,
-                              value_heads=self.value_heads, sink_values=self.sink_values)
+                              value_heads=self.value_heads, sink_values=self.sink_values, keep_first=self.keep_first)
 
     def _prepare_unfused(self, qkv, q, cache, ctx, table, qw, kw, eps) -> None:
         """A position encoding without kernel tables: norm, then `apply_`, then the cache write."""
@@ -300,7 +370,7 @@ def _prefill_tcgen05_kernel(part, q, cache, out, ctx, table) -> bool:
 
 def _prefill_capped_kernel(part, q, cache, out, ctx, table) -> bool:
     """Capped scores, chunks, a sink, values of their own size: the tiled tensor-core kernel for those."""
-    if part.plain or not ops.attention_capped_fits(part.head_dim, part.value_dim, part.window, 1):
+    if part.plain or part.keep_first or not ops.attention_capped_fits(part.head_dim, part.value_dim, part.window, 1):
         return False
     ops.attention_capped_prefill(q, cache.keys, cache.values, out, ctx.seq_start, ctx.seq_pos0, table, ctx.n_seqs, ctx.max_new,
                                  part.num_heads, part.num_kv_heads, part.head_dim, part.value_dim, part.scale, part.softcap,
@@ -312,7 +382,7 @@ def _prefill_capped_kernel(part, q, cache, out, ctx, table) -> bool:
 def _prefill_capped_tcgen05_kernel(part, q, cache, out, ctx, table) -> bool:
     """The same on tcgen05 with TMA-fed tiles: head sizes 64 and 128, values as wide as keys, and enough new tokens
     for 128-row tiles to be worth it."""
-    if part.plain or part.shared_values or not ops.attention_capped_prefill_tc_fits(part.head_dim, part.value_dim, part.window) \
+    if part.plain or part.keep_first or part.shared_values or not ops.attention_capped_prefill_tc_fits(part.head_dim, part.value_dim, part.window) \
             or ctx.max_new < tc_prefill_rows or part.scale <= 0 or part.sink_values is not None:
         return False
     ops.attention_capped_prefill_tc(q[:ctx.n_tokens], cache.keys, cache.values, out, ctx.seq_start, ctx.seq_pos0, table,
@@ -324,7 +394,7 @@ def _prefill_capped_tcgen05_kernel(part, q, cache, out, ctx, table) -> bool:
 def _decode_capped_kernel(part, q, cache, out, ctx, table) -> bool:
     """The same for decode steps: split over the keys of the chunk (or of the whole context), merged with the sink."""
     nq, nkv = part.num_heads, part.num_kv_heads
-    if part.plain or not ops.attention_capped_fits(part.head_dim, part.value_dim, part.window, nq // nkv):
+    if part.plain or part.keep_first or not ops.attention_capped_fits(part.head_dim, part.value_dim, part.window, nq // nkv):
         return False
     splits = ops.attention_capped_splits(ctx.n_tokens, nkv, _sm_count(ctx.device),
                                          min(part.chunk or part.window or ctx.max_context, ctx.max_context))

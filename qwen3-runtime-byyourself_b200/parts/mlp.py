@@ -25,11 +25,13 @@ TENSOR_NAMES = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "dow
 
 class SwiGLU(Part):
     def __init__(self, hidden_size: int, intermediate_size: int, prefix: str = "", activation: str = "silu",
-                 names: Optional[dict] = None):
-        if activation not in ops.ACTIVATIONS:
-            raise ValueError(f"activation {activation!r}: one of {sorted(ops.ACTIVATIONS)}")
+                 names: Optional[dict] = None, limit: float = float("inf"), alpha: float = 1.702):
+        """`activation="clamped"`: down( g sigmoid(alpha g) (u + 1) ) with g = min(gate, limit), u = clamp(up, -limit, limit),
+        the form of the routed experts (parts/moe.py) as a dense feed-forward."""
+        if activation not in ops.ACTIVATIONS and activation != "clamped":
+            raise ValueError(f"activation {activation!r}: 'clamped' or one of {sorted(ops.ACTIVATIONS)}")
         self.hidden_size, self.intermediate_size, self.prefix = int(hidden_size), int(intermediate_size), prefix
-        self.activation = activation
+        self.activation, self.limit, self.alpha = activation, float(limit), float(alpha)
         self.names = dict(TENSOR_NAMES, **(names or {}))
         self.w_gate_up = self.w_down = None
 
@@ -49,7 +51,7 @@ class SwiGLU(Part):
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         N, I = ctx.n_tokens, self.intermediate_size
         act = ctx.scratch.get("ff.act", (N, I), ctx.dtype)
-        fused = self.interleaved and ctx.dtype == torch.bfloat16 and self.hidden_size % 8 == 0
+        fused = self.interleaved and ctx.dtype == torch.bfloat16 and self.hidden_size % 8 == 0 and self.activation != "clamped"
         if fused and N <= linear_module.skinny_rows:
             ops.gemm_skinny_gated(x, self.w_gate_up, act, self.activation)   # product, activation and gating in one kernel
         elif fused and linear_module.tcgen05_form(N, 2 * I, self.hidden_size, gated=True) == "weights_first":
@@ -60,7 +62,10 @@ class SwiGLU(Part):
         else:
             gate_up = ctx.scratch.get("ff.gate_up", (N, 2 * I), ctx.dtype)
             linear(x, self.w_gate_up, gate_up)
-            ops.silu_mul(gate_up, act, self.interleaved, self.activation)
+            if self.activation == "clamped":
+                ops.clamped_mul(gate_up, act, self.limit, self.alpha, self.interleaved)
+            else:
+                ops.silu_mul(gate_up, act, self.interleaved, self.activation)
         out = ctx.scratch.get("ff.out", (N, self.hidden_size), ctx.dtype)
         return linear(act, self.w_down, out)
 

@@ -61,6 +61,17 @@ class WeightError(ValueError):
         super().__init__("\n".join(lines))
 
 
+def resolve_sizes(ckpt: Checkpoint, specs: Dict[str, WeightSpec]) -> Dict[str, WeightSpec]:
+    """`specs` with every size that a model leaves open (-1: the configuration does not give it, the tensor's shape does)
+    taken from the checkpoint's header.  The number of dimensions still has to agree."""
+    out = dict(specs)
+    for name, spec in specs.items():
+        info = ckpt.tensors.get(name)
+        if info is not None and -1 in spec.shape and len(info.shape) == len(spec.shape):
+            out[name] = WeightSpec(tuple(int(f) if s == -1 else s for s, f in zip(spec.shape, info.shape)), spec.role)
+    return out
+
+
 def check_checkpoint(ckpt: Checkpoint, folder: str, specs: Dict[str, WeightSpec], ignorable: Iterable[str] = ()) -> None:
     """Raise the one `WeightError` that lists everything in which the checkpoint and the model's own list of
     tensors differ; nothing is read beyond the headers."""
@@ -86,6 +97,7 @@ def load_weights(folder: str, specs: Dict[str, WeightSpec], ignorable: Iterable[
     """Read the tensors named by `specs` from `folder`, in their stored dtypes, onto `device` (each as a tensor
     of its own; a model that is bound for a device goes through `open_upload` instead)."""
     ckpt = Checkpoint(folder)
+    specs = resolve_sizes(ckpt, specs)
     check_checkpoint(ckpt, folder, specs, ignorable)
     out = {}
     for name in specs:
@@ -99,6 +111,7 @@ def open_upload(folder: str, specs: Dict[str, WeightSpec], ignorable: Iterable[s
     from the mapped file to its final place on the device in one pass (weights/upload.py)."""
     from .upload import CheckpointUpload
     ckpt = Checkpoint(folder)
+    specs = resolve_sizes(ckpt, specs)
     check_checkpoint(ckpt, folder, specs, ignorable)
     return CheckpointUpload(ckpt, specs, dtype, device, warn)
 
@@ -114,6 +127,8 @@ def random_weights(specs: Dict[str, WeightSpec], seed: int, dtype: torch.dtype =
     for name, spec in specs.items():
         gen = torch.Generator(device=device)
         gen.manual_seed(_stream_seed(seed, name))
+        if -1 in spec.shape:
+            raise ValueError(f"{name}: the configuration leaves a size of this tensor to the checkpoint; random weights need it")
         if spec.role == "int_table":
             out[name] = torch.zeros(spec.shape, dtype=torch.int32, device=device)
             continue
