@@ -88,14 +88,15 @@ class FedinexConfig:
                 self._check_heads(m, w)
                 if not _get(m, "tau", float, w) > 0:
                     raise ConfigError(f"{w}tau must be positive")
-                if (_opt(m, "rank", int, w) or 1) <= 0:
+                rank = _opt(m, "rank", int, w)
+                if rank is not None and rank <= 0:
                     raise ConfigError(f"{w}rank must be positive")
             elif kind == "attention":
                 self._check_attention(m, w)
                 if _opt(m, "v_mix", bool, w):
-                    width = m["kv_heads"] * m["vdim"]
+                    width = (m["kv_heads"], m["vdim"])
                     if mixed_width not in (None, width):
-                        raise ConfigError(f"{w}v_mix: every layer that blends values has kv_heads * vdim = {mixed_width}")
+                        raise ConfigError(f"{w}v_mix: every layer that blends values has (kv_heads, vdim) = {mixed_width}")
                     mixed_width = width
             elif kind == "parallel":
                 self._check_attention(_get(m, "left", dict, w), w + "left.")
