@@ -5,6 +5,7 @@ model with random weights in bfloat16 on one B200, batch 8 at a context of 4,096
     python bench.py --designs        (another measurement: a Dozazen model beside Qwen3 at equal sizes)
     python bench.py --designs lagulorn   (the same for a Lagulorn model)
     python bench.py --designs fagunex    (a Fagunex model beside the Lagulorn model of the same widths)
+    python bench.py --designs fedinex    (a Fedinex model beside the Fagunex model of the same widths)
 
 Prints ONE JSON line.  A "step" is one decode step of the whole batch.
   value     decoded tokens a second, timed on the device with CUDA events around K steps;
@@ -484,6 +485,43 @@ def fagunex_side_by_side(q, torch, Sampler, steps, warmup, batch=8, context=4096
     return out
 
 
+def fedinex_config(width, heads, kv, d, ff, layers, window=1024, keep_first=4, experts=16, top=2):
+    """A Fedinex model of the widths of the Fagunex model beside it: gated linear attention (width / d heads of d x d, a decay
+    through a projection of rank 64); attention with biases, a window of `window` keys that keeps the first `keep_first`, half of
+    every head rotated and values blended from the first such layer on; attention over every earlier key (a convolution of four
+    taps on q, k and v, a gate per head) beside a matrix memory of width / (2 d) heads of d x d; the windowed attention again; and
+    so on.  The first layer's feed-forward is dense, the others routed (`experts` experts of ff / (2 top), `top` per token,
+    four groups of which two are kept)."""
+    rot = {"base": 1000000.0, "dims": d // 2}
+    linear = {"type": "gla", "mixer": {"heads": width // d, "dim": d, "vdim": d, "tau": 16.0, "rank": 64}}
+    windowed = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv, "dim": d, "vdim": d, "scale": d ** -0.5, "rot": rot,
+                                                "mask": {"size": window, "keep_first": keep_first}, "v_mix": True}}
+    both = {"type": "parallel", "mixer": {"left": {"heads": heads, "kv_heads": kv, "dim": d, "vdim": d, "scale": d ** -0.5, "rot": rot, "conv": 4},
+                                           "right": {"heads": max(width // (2 * d), 1), "dim": d, "vdim": d, "gate_cap": 15.0},
+                                           "left_scale": 0.6, "right_scale": 0.9}}
+    moe = {"kind": "moe", "expert": {"ff": ff // (2 * top), "limit": 7.0},
+           "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+    order = [linear, windowed, both, windowed]
+    return {"architecture": "Fedinex", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-6},
+            "layers": [dict(order[i % 4], mlp={"kind": "dense", "ff": ff, "limit": 7.0} if i == 0 else moe) for i in range(layers)]}
+
+
+def fedinex_side_by_side(q, torch, Sampler, steps, warmup, batch=8, context=4096):
+    """Fedinex beside Fagunex, the closest of the other designs (a 32-bit hidden state, attention with a window in turn with a
+    recurrence whose state a scan carries, routed experts), at equal widths (random weights, bfloat16): decode at `batch` x
+    `context`, a prompt step of 2,048 tokens, and the time of every kernel of one step of each kind."""
+    import numpy as np
+    out = {"batch": batch, "context": context, "prompt_tokens": PREFILL_TOKENS, "vocab": DESIGN_VOCAB, "sizes": {}}
+    for name, width, heads, kv, d, ff, layers in DESIGN_SIZES:
+        row = {"width": width, "heads": heads, "kv_heads": kv, "head_dim": d, "ff": ff, "layers": layers}
+        row["fedinex"] = design_point(q, torch, Sampler, fedinex_config(width, heads, kv, d, ff, layers), np.random.default_rng(0),
+                                      batch, context, steps, warmup)
+        row["fagunex"] = design_point(q, torch, Sampler, fagunex_config(width, heads, d, ff, layers), np.random.default_rng(0),
+                                      batch, context, steps, warmup)
+        out["sizes"][name] = row
+    return out
+
+
 def designs_side_by_side(q, torch, Sampler, steps, warmup, batch=8, context=4096):
     """Dozazen beside Qwen3 at equal sizes (random weights, bfloat16): decode at `batch` x `context`, a prompt step of
     2,048 tokens; chunks longer than the context (every key is read, as in Qwen3) and chunks of 1,024."""
@@ -519,7 +557,7 @@ def main() -> int:
     ap.add_argument("--kernels", action="store_true",
                     help="instead of the benchmark: time every kernel of one decode step and of one 2,048-token prompt step "
                          "with CUDA events (steps launched afresh, not replayed) and print the sums per entry point")
-    ap.add_argument("--designs", nargs="?", const="dozazen", default=None, choices=["dozazen", "lagulorn", "fagunex"],
+    ap.add_argument("--designs", nargs="?", const="dozazen", default=None, choices=["dozazen", "lagulorn", "fagunex", "fedinex"],
                     help="instead of the benchmark: decode and prompt throughput of a Dozazen (default) or Lagulorn model beside "
                          "the Qwen3 model of the same widths (or of a Fagunex model beside the Lagulorn one) at two sizes, with the "
                          "time of every kernel of one step of each kind")
@@ -543,7 +581,8 @@ def main() -> int:
     cfg, CONTEXT, shape_batch = SHAPES[args.shape]
     if args.designs:
         torch.cuda.set_device(0)
-        side_by_side = {"lagulorn": lagulorn_side_by_side, "fagunex": fagunex_side_by_side}.get(args.designs, designs_side_by_side)
+        side_by_side = {"lagulorn": lagulorn_side_by_side, "fagunex": fagunex_side_by_side,
+                        "fedinex": fedinex_side_by_side}.get(args.designs, designs_side_by_side)
         print(json.dumps(side_by_side(q, torch, Sampler, min(args.steps, 64), warmup, args.batch or 8, args.context or 4096)))
         return 0
     if args.products:

@@ -4,6 +4,8 @@
 //
 //     s_j = cap * tanh(q.k_j * scale / cap)         (cap = 0: s_j = q.k_j * scale)
 //     j visible from i:  j <= i  and  floor(j / chunk) == floor(i / chunk)       (chunk = 0: j <= i)
+//                        or, with a window: j <= i  and  (i - j < window  or  j < keep), keep the number of first keys
+//                        of a sequence that stay visible (their pages are walked before the window's)
 //     p_j = exp(s_j) / (sink + sum_visible exp(s_j)),  sink = 1 or 0
 //     o   = sum_j p_j v_j
 //
@@ -121,7 +123,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 prefill_capped_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                       TO* __restrict__ out, const int* __restrict__ seq_start, const int* __restrict__ seq_pos0,
                       const int* __restrict__ page_table, int pages_per_seq, int nq, int nkv, float scale, float cap, int chunk,
-                      int sink, int nv, const float* __restrict__ sink_values) {
+                      int sink, int nv, const float* __restrict__ sink_values, int keep) {
     extern __shared__ __align__(16) unsigned char smem[];
     pdl_launch_dependents();
     pdl_wait();
@@ -160,29 +162,35 @@ prefill_capped_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pag
 
     const int last_row = min(tile * BM + BM, n_new) - 1;
     const int pg_begin = chunk_start(pos0 + tile * BM, chunk) / PAGE, pg_end = (pos0 + last_row) / PAGE + 1;
+    // with a window, the first `keep` keys of the sequence stay visible: the pages that hold them and lie before the
+    // window's come first; step i of the walk is page i if i < n_keep, else page pg_begin + i - n_keep
+    const int n_keep = min((keep + PAGE - 1) / PAGE, pg_begin), n_walk = n_keep + pg_end - pg_begin;
     const int warp_first_pos = pos0 + tile * BM + warp * 16;                   // lowest position of the warp's rows
     const int warp_first_key = chunk_start(warp_first_pos, chunk);             // no row of the warp sees a key before it
     const int warp_last_start = chunk_start(warp_first_pos + 15, chunk);       // from here on every row of the warp may see
     const uint32_t base = smem_u32(smem);
 
-    auto issue = [&](int pg) {
-        if (pg < pg_end) {
+    auto issue = [&](int i) {
+        if (i < n_walk) {
+            const int pg = i < n_keep ? i : pg_begin + i - n_keep;
             const int64_t k_at = ((int64_t)pages[pg] * nkv + kvh) * PAGE, v_at = ((int64_t)pages[pg] * nv + vh) * PAGE;
-            const uint32_t dst = base + ((pg - pg_begin) & 1) * (K_TILE + V_TILE);
+            const uint32_t dst = base + (i & 1) * (K_TILE + V_TILE);
             load_rows<PAGE, D, K_ROW, WARPS * 32>(dst, k_pages + k_at * D, threadIdx.x);
             load_rows<PAGE, VD, V_ROW, WARPS * 32>(dst + K_TILE, v_pages + v_at * VD, threadIdx.x);
         }
         cp_async_commit();
     };
-    issue(pg_begin);
-    for (int pg = pg_begin; pg < pg_end; ++pg) {
-        issue(pg + 1);              // into the other stage, which every warp left before the last barrier
+    issue(0);
+    for (int i = 0; i < n_walk; ++i) {
+        issue(i + 1);               // into the other stage, which every warp left before the last barrier
         cp_async_wait<1>();
         __syncthreads();
-        const uint32_t kbuf = base + ((pg - pg_begin) & 1) * (K_TILE + V_TILE), vbuf = kbuf + K_TILE;
+        const int pg = i < n_keep ? i : pg_begin + i - n_keep;
+        const uint32_t kbuf = base + (i & 1) * (K_TILE + V_TILE), vbuf = kbuf + K_TILE;
         const int key_base = pg * PAGE;
         // a warp whose rows all lie before this page, or whose chunks all start behind it, has nothing to see in it
-        if (key_base <= warp_first_pos + 15 && key_base + PAGE > warp_first_key) {
+        // (but for the kept keys)
+        if (key_base <= warp_first_pos + 15 && (key_base + PAGE > warp_first_key || key_base < keep)) {
             float s[8][4];
 #pragma unroll
             for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
@@ -206,7 +214,7 @@ prefill_capped_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pag
                     float v = score_log2(s[j][e], scale, cap, inv_cap);
                     if (edge) {
                         const int key = key_base + j * 8 + tq * 2 + (e & 1);
-                        const bool seen = (e >> 1) ? (key <= p_hi && key >= c_hi) : (key <= p_lo && key >= c_lo);
+                        const bool seen = (e >> 1) ? (key <= p_hi && (key >= c_hi || key < keep)) : (key <= p_lo && (key >= c_lo || key < keep));
                         v = seen ? v : -INFINITY;
                     }
                     s[j][e] = v;
@@ -326,7 +334,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 decode_capped_split_kernel(const bf16* __restrict__ q, const bf16* k_pages, const bf16* v_pages,
                            float* __restrict__ part, const int* __restrict__ token_seq, const int* __restrict__ token_pos,
                            const int* __restrict__ page_table, int pages_per_seq, int nq, int nkv, float scale, float cap,
-                           int chunk, const FusedArgs fused, int nv) {
+                           int chunk, const FusedArgs fused, int nv, int keep) {
     extern __shared__ __align__(16) unsigned char smem[];
     pdl_launch_dependents();
     pdl_wait();
@@ -337,17 +345,22 @@ decode_capped_split_kernel(const bf16* __restrict__ q, const bf16* k_pages, cons
     const int* pages = page_table + (int64_t)token_seq[t] * pages_per_seq;
     const float inv_cap = cap > 0.0f ? 1.0f / cap : 0.0f;
     const int lo = chunk_start(pos, chunk);
-    const int first_page = lo / PAGE, n_pages = pos / PAGE + 1 - first_page;
+    // with a window, the pages of the first `keep` keys that lie before the window's pages are walked first: step x of
+    // the walk is page x if x < n_keep, else page first_page + x - n_keep; the splits share the steps
+    const int first_page = lo / PAGE, n_keep = min((keep + PAGE - 1) / PAGE, first_page);
+    const int n_pages = n_keep + pos / PAGE + 1 - first_page;
     const int per_split = (n_pages + n_splits - 1) / n_splits;
-    const int pg_begin = first_page + split * per_split;
-    const int pg_end = min(first_page + n_pages, pg_begin + per_split);
+    const int pg_begin = split * per_split;
+    const int pg_end = min(n_pages, pg_begin + per_split);
     const int count = max(pg_end - pg_begin, 0);
+    auto page_of = [&](int x) { return x < n_keep ? x : first_page + x - n_keep; };
 
     const uint32_t pipe = smem_u32(smem) + warp * (STAGES * (K_PANEL + V_PANEL));
     auto issue = [&](int i) {
         if (i < count) {
-            const int64_t at = ((int64_t)pages[pg_begin + i] * nkv + kvh) * PAGE + warp * KEYS_PER_WARP;
-            const int64_t v_at = ((int64_t)pages[pg_begin + i] * nv + kvh / (nkv / nv)) * PAGE + warp * KEYS_PER_WARP;
+            const int page = pages[page_of(pg_begin + i)];
+            const int64_t at = ((int64_t)page * nkv + kvh) * PAGE + warp * KEYS_PER_WARP;
+            const int64_t v_at = ((int64_t)page * nv + kvh / (nkv / nv)) * PAGE + warp * KEYS_PER_WARP;
             const uint32_t dst = pipe + (i % STAGES) * (K_PANEL + V_PANEL);
             load_rows<KEYS_PER_WARP, D, K_ROW, 32>(dst, k_pages + at * D, lane);
             load_rows<KEYS_PER_WARP, VD, V_ROW, 32>(dst + K_PANEL, v_pages + v_at * VD, lane);
@@ -358,7 +371,7 @@ decode_capped_split_kernel(const bf16* __restrict__ q, const bf16* k_pages, cons
     for (int s = 0; s < STAGES - 1; ++s) issue(s);
 
     // the block that holds the token's own page owns the new key and value
-    const bool owner = FUSED && count > 0 && pg_end == first_page + n_pages;
+    const bool owner = FUSED && count > 0 && pg_end == n_pages;
     bf16* prep_q = reinterpret_cast<bf16*>(smem + DECODE_SMEM);          // [16][D]
     bf16* new_k = prep_q + 16 * D;                                       // [D]
     bf16* new_v = new_k + D;                                             // [VD]
@@ -431,14 +444,14 @@ decode_capped_split_kernel(const bf16* __restrict__ q, const bf16* k_pages, cons
             mma_bf16(s[1], qa[kt], b[2], b[3]);
         }
         // key index of s[j][e]: page*64 + warp*16 + j*8 + tq*2 + (e & 1); keys outside [lo, pos] are not seen
-        const int key0 = (pg_begin + i) * PAGE + warp * KEYS_PER_WARP + tq * 2;
+        const int key0 = page_of(pg_begin + i) * PAGE + warp * KEYS_PER_WARP + tq * 2;
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int j = 0; j < 2; ++j)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int key = key0 + j * 8 + (e & 1);
-                const float v = (key >= lo && key <= last_key) ? score_log2(s[j][e], scale, cap, inv_cap) : -INFINITY;
+                const float v = ((key >= lo || key < keep) && key <= last_key) ? score_log2(s[j][e], scale, cap, inv_cap) : -INFINITY;
                 s[j][e] = v;
                 mx[e >> 1] = fmaxf(mx[e >> 1], v);
             }
@@ -572,8 +585,9 @@ Q3_EXPORT int q3_attention_capped_prefill_bf16(const void* q, const void* k_page
                                                const int* seq_start, const int* seq_pos0, const int* page_table,
                                                int pages_per_seq, int n_seqs, int max_new, int nq, int nkv, float scale,
                                                float softcap, int chunk, int sink, int window, int value_heads, int out_f32,
-                                               const float* sink_values, void* stream) {
+                                               const float* sink_values, int keep_first, void* stream) {
     if (n_seqs <= 0 || max_new <= 0) return 0;
+    if (keep_first < 0 || (keep_first > 0 && window <= 0)) return Q3_ERR_BAD_SIZE;
     if (value_heads <= 0) value_heads = nkv;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nkv % value_heads != 0 || softcap < 0.0f || chunk < 0 || window < 0 ||
         (chunk > 0 && window > 0))
@@ -587,13 +601,13 @@ Q3_EXPORT int q3_attention_capped_prefill_bf16(const void* q, const void* k_page
         if (e != cudaSuccess) return (int)e;
         return (int)q3_launch(prefill_capped_kernel<float>, grid, dim3(WARPS * 32), PREFILL_SMEM, (cudaStream_t)stream, (const bf16*)q,
                               (const bf16*)k_pages, (const bf16*)v_pages, (float*)out, seq_start, seq_pos0, page_table,
-                              pages_per_seq, nq, nkv, scale, softcap, span, sink, value_heads, sink_values);
+                              pages_per_seq, nq, nkv, scale, softcap, span, sink, value_heads, sink_values, keep_first);
     }
     cudaError_t e = q3_allow_shared_memory(prefill_capped_kernel<bf16>, PREFILL_SMEM, configured[0]);
     if (e != cudaSuccess) return (int)e;
     return (int)q3_launch(prefill_capped_kernel<bf16>, grid, dim3(WARPS * 32), PREFILL_SMEM, (cudaStream_t)stream, (const bf16*)q,
                           (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, seq_start, seq_pos0, page_table,
-                          pages_per_seq, nq, nkv, scale, softcap, span, sink, value_heads, sink_values);
+                          pages_per_seq, nq, nkv, scale, softcap, span, sink, value_heads, sink_values, keep_first);
 }
 
 // One new token per sequence: scratch holds n_tokens * nq * n_splits * (VD + 2) float32.
@@ -601,8 +615,9 @@ Q3_EXPORT int q3_attention_capped_decode_bf16(const void* q, const void* k_pages
                                               const int* token_seq, const int* token_pos, const int* page_table,
                                               int pages_per_seq, int64_t n_tokens, int nq, int nkv, float scale, float softcap,
                                               int chunk, int sink, int n_splits, int window, int value_heads, int out_f32,
-                                              const float* sink_values, void* stream) {
+                                              const float* sink_values, int keep_first, void* stream) {
     if (n_tokens <= 0) return 0;
+    if (keep_first < 0 || (keep_first > 0 && window <= 0)) return Q3_ERR_BAD_SIZE;
     if (value_heads <= 0) value_heads = nkv;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq / nkv > 16 || nkv % value_heads != 0 || softcap < 0.0f || chunk < 0 ||
         window < 0 || (chunk > 0 && window > 0) || n_splits <= 0)
@@ -617,7 +632,7 @@ Q3_EXPORT int q3_attention_capped_decode_bf16(const void* q, const void* k_pages
     FusedArgs none = {};
     cudaError_t e = q3_launch(decode_capped_split_kernel<false>, dim3(n_splits, nkv, (unsigned)n_tokens), dim3(WARPS * 32), DECODE_SMEM,
                               (cudaStream_t)stream, (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, scratch, token_seq,
-                              token_pos, page_table, pages_per_seq, nq, nkv, scale, softcap, span, none, value_heads);
+                              token_pos, page_table, pages_per_seq, nq, nkv, scale, softcap, span, none, value_heads, keep_first);
     if (e != cudaSuccess) return (int)e;
     if (out_f32)
         return (int)q3_launch(decode_capped_merge_kernel<float>, dim3(nq, (unsigned)n_tokens), dim3(VD >= 128 ? 128 : 64), 0,
@@ -648,7 +663,7 @@ Q3_EXPORT int q3_attention_capped_decode_fused_bf16(const void* qkv, void* k_pag
     fused.rot = rotary_dim > 0 ? rotary_dim : D;
     cudaError_t e = q3_launch(decode_capped_split_kernel<true>, dim3(n_splits, nkv, (unsigned)n_tokens), dim3(WARPS * 32),
                               DECODE_SMEM_FUSED, (cudaStream_t)stream, (const bf16*)nullptr, (const bf16*)k_pages, (const bf16*)v_pages,
-                              scratch, token_seq, token_pos, page_table, pages_per_seq, nq, nkv, scale, softcap, chunk, fused, nkv);
+                              scratch, token_seq, token_pos, page_table, pages_per_seq, nq, nkv, scale, softcap, chunk, fused, nkv, 0);
     if (e != cudaSuccess) return (int)e;
     return (int)q3_launch(decode_capped_merge_kernel<bf16>, dim3(nq, (unsigned)n_tokens), dim3(VD >= 128 ? 128 : 64), 0,
                           (cudaStream_t)stream, (const float*)scratch, (bf16*)out, nq, n_splits, sink, (const float*)nullptr);

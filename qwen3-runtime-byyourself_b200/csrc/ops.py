@@ -794,9 +794,9 @@ def _capped_defines(d: int, vd: int):
 def attention_capped_prefill(q, k_pages, v_pages, out, seq_start, seq_pos0, page_table, n_seqs: int, max_new: int, nq: int,
                              nkv: int, d: int, vd: int, scale: float, softcap: float = 0.0, chunk: Optional[int] = None,
                              sink: bool = False, window: Optional[int] = None, value_heads: Optional[int] = None,
-                             sink_values: Optional[torch.Tensor] = None):
+                             sink_values: Optional[torch.Tensor] = None, keep_first: int = 0):
     """Attention of every new token of every sequence over its pages (bfloat16, tiled, tensor cores) with capped scores,
-    chunked visibility or a sliding window, and a sink (its score per query head in `sink_values`, else 0); q [tokens, nq * d], out [tokens, nq * vd] in bfloat16 or float32;
+    chunked visibility or a sliding window (beside which the first `keep_first` keys of the sequence stay visible), and a sink (its score per query head in `sink_values`, else 0); q [tokens, nq * d], out [tokens, nq * vd] in bfloat16 or float32;
     `value_heads`: the number of value heads if not `nkv` (each serves nkv / value_heads key heads)."""
     nv = int(value_heads or nkv)
     if q.dtype != torch.bfloat16 or not attention_capped_fits(d, vd, None, 1) or out.dtype not in (torch.bfloat16, torch.float32):
@@ -805,13 +805,13 @@ def attention_capped_prefill(q, k_pages, v_pages, out, seq_start, seq_pos0, page
         raise KernelError("attention_capped_prefill: shapes do not fit")
     fn = _fn("attention_capped.cu", "q3_attention_capped_prefill_bf16",
              [c_void_p] * 7 + [c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                               c_void_p],
+                               c_int, c_void_p],
              defines=_capped_defines(d, vd))
     _check(fn(_dev(q, "q"), _dev(k_pages, "k_pages", torch.bfloat16), _dev(v_pages, "v_pages", torch.bfloat16),
               _dev(out, "out"), _dev(seq_start, "seq_start", torch.int32),
               _dev(seq_pos0, "seq_pos0", torch.int32), _dev(page_table, "page_table", torch.int32), page_table.shape[-1],
               n_seqs, max_new, nq, nkv, float(scale), float(softcap or 0.0), int(chunk or 0), int(bool(sink)), int(window or 0), nv,
-              int(out.dtype == torch.float32), _sink_ptr(sink, sink_values, nq), _stream()),
+              int(out.dtype == torch.float32), _sink_ptr(sink, sink_values, nq), int(keep_first or 0) if window else 0, _stream()),
            "attention_capped_prefill")
     return out
 
@@ -825,7 +825,7 @@ def attention_capped_splits(n_tokens: int, nkv: int, sm_count: int, max_keys: in
 def attention_capped_decode(q, k_pages, v_pages, out, scratch, token_seq, token_pos, page_table, n_tokens: int, nq: int,
                             nkv: int, d: int, vd: int, scale: float, softcap: float, chunk: Optional[int], sink: bool,
                             n_splits: int, window: Optional[int] = None, value_heads: Optional[int] = None,
-                            sink_values: Optional[torch.Tensor] = None):
+                            sink_values: Optional[torch.Tensor] = None, keep_first: int = 0):
     """The same for one new token per sequence, the keys split over `n_splits` blocks per (token, kv head); `scratch`
     holds n_tokens * nq * n_splits * (vd + 2) float32."""
     nv = int(value_heads or nkv)
@@ -836,14 +836,15 @@ def attention_capped_decode(q, k_pages, v_pages, out, scratch, token_seq, token_
         raise KernelError("attention_capped_decode: shapes do not fit")
     fn = _fn("attention_capped.cu", "q3_attention_capped_decode_bf16",
              [c_void_p] * 8 + [c_int, c_int64, c_int, c_int, c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                               c_void_p],
+                               c_int, c_void_p],
              defines=_capped_defines(d, vd))
     _check(fn(_dev(q, "q"), _dev(k_pages, "k_pages", torch.bfloat16), _dev(v_pages, "v_pages", torch.bfloat16),
               _dev(out, "out"), _dev(scratch, "scratch", torch.float32),
               _dev(token_seq, "token_seq", torch.int32), _dev(token_pos, "token_pos", torch.int32),
               _dev(page_table, "page_table", torch.int32), page_table.shape[-1], n_tokens, nq, nkv, float(scale),
               float(softcap or 0.0), int(chunk or 0), int(bool(sink)), int(n_splits), int(window or 0), nv,
-              int(out.dtype == torch.float32), _sink_ptr(sink, sink_values, nq), _stream()), "attention_capped_decode")
+              int(out.dtype == torch.float32), _sink_ptr(sink, sink_values, nq), int(keep_first or 0) if window else 0, _stream()),
+           "attention_capped_decode")
     _count_extra(1)                                              # the split kernel and the merge kernel
     return out
 

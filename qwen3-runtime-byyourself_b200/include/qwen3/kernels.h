@@ -123,14 +123,15 @@ int q3_attention_capped_value_dim(void);
 int q3_attention_capped_prefill_bf16(const void* q, const void* k_pages, const void* v_pages, void* out, const int* seq_start,
                                      const int* seq_pos0, const int* page_table, int pages_per_seq, int n_seqs, int max_new, int nq,
                                      int nkv, float scale, float softcap, int chunk, int sink, int window, int value_heads,
-                                     int out_f32, const float* sink_values, void* stream);
-/* (window > 0: a sliding window of that many keys instead of chunks; value_heads 0 = nkv, else each value head serves
-   nkv / value_heads key heads; out_f32: `out` is float; sink_values (may be null): the sink's score per query head) */
+                                     int out_f32, const float* sink_values, int keep_first, void* stream);
+/* (window > 0: a sliding window of that many keys instead of chunks, beside which the first keep_first keys of the sequence
+   stay visible; value_heads 0 = nkv, else each value head serves nkv / value_heads key heads; out_f32: `out` is float;
+   sink_values (may be null): the sink's score per query head) */
 /* one new token per sequence; scratch: n_tokens * nq * n_splits * (value_dim + 2) float32 */
 int q3_attention_capped_decode_bf16(const void* q, const void* k_pages, const void* v_pages, void* out, float* scratch,
                                     const int* token_seq, const int* token_pos, const int* page_table, int pages_per_seq,
                                     int64_t n_tokens, int nq, int nkv, float scale, float softcap, int chunk, int sink, int n_splits,
-                                    int window, int value_heads, int out_f32, const float* sink_values, void* stream);
+                                    int window, int value_heads, int out_f32, const float* sink_values, int keep_first, void* stream);
 
 /* ---- attention_decode.cu (-DQ3_HEAD_DIM): one new token per sequence, bfloat16 ---------------------------- */
 int q3_attention_decode_head_dim(void);

@@ -57,6 +57,12 @@ TENSOR_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight"
 
 
 class GQAAttention(Part):
+    # what a part that builds on this one without its constructor still finds (the options beyond plain attention are off)
+    out_name = "mixer.out"
+    keep_first, out_bias, value_mix, conv_taps, head_gate = 0, False, None, 0, False
+    o_bias = bias_v = conv_weight = w_gate = None
+    mix_lambda = 0.0
+
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                  qk_norm: Optional[PartSpec] = None, position: Optional[PartSpec] = None,
                  window: Optional[int] = None, prefix: str = "", value_dim: Optional[int] = None, bias: bool = False,
@@ -370,12 +376,12 @@ def _prefill_tcgen05_kernel(part, q, cache, out, ctx, table) -> bool:
 
 def _prefill_capped_kernel(part, q, cache, out, ctx, table) -> bool:
     """Capped scores, chunks, a sink, values of their own size: the tiled tensor-core kernel for those."""
-    if part.plain or part.keep_first or not ops.attention_capped_fits(part.head_dim, part.value_dim, part.window, 1):
+    if part.plain or not ops.attention_capped_fits(part.head_dim, part.value_dim, part.window, 1):
         return False
     ops.attention_capped_prefill(q, cache.keys, cache.values, out, ctx.seq_start, ctx.seq_pos0, table, ctx.n_seqs, ctx.max_new,
                                  part.num_heads, part.num_kv_heads, part.head_dim, part.value_dim, part.scale, part.softcap,
                                  part.chunk, part.sink, window=part.window, value_heads=part.value_heads,
-                                 sink_values=part.sink_values)
+                                 sink_values=part.sink_values, keep_first=part.keep_first)
     return True
 
 
@@ -394,14 +400,15 @@ def _prefill_capped_tcgen05_kernel(part, q, cache, out, ctx, table) -> bool:
 def _decode_capped_kernel(part, q, cache, out, ctx, table) -> bool:
     """The same for decode steps: split over the keys of the chunk (or of the whole context), merged with the sink."""
     nq, nkv = part.num_heads, part.num_kv_heads
-    if part.plain or part.keep_first or not ops.attention_capped_fits(part.head_dim, part.value_dim, part.window, nq // nkv):
+    if part.plain or not ops.attention_capped_fits(part.head_dim, part.value_dim, part.window, nq // nkv):
         return False
     splits = ops.attention_capped_splits(ctx.n_tokens, nkv, _sm_count(ctx.device),
-                                         min(part.chunk or part.window or ctx.max_context, ctx.max_context))
+                                         min(part.chunk or (part.window or 0) + part.keep_first or ctx.max_context, ctx.max_context))
     scratch = ctx.scratch.get("attn.capped_scratch", (ctx.n_tokens * nq * splits * (part.value_dim + 2),), torch.float32)
     ops.attention_capped_decode(q, cache.keys, cache.values, out, scratch, ctx.token_seq, ctx.token_pos, table, ctx.n_tokens,
                                 nq, nkv, part.head_dim, part.value_dim, part.scale, part.softcap, part.chunk, part.sink, splits,
-                                window=part.window, value_heads=part.value_heads, sink_values=part.sink_values)
+                                window=part.window, value_heads=part.value_heads, sink_values=part.sink_values,
+                                keep_first=part.keep_first)
     return True
 
 

@@ -294,10 +294,57 @@ def plant_attention(rng, lengths, H, G, d, vd, window, keep, back, peak):
     return seqs
 
 
+WHERE = {"edge_in": lambda p, window, keep: window - 1, "edge_out": lambda p, window, keep: window,
+         "kept_in": lambda p, window, keep: p - (keep - 1), "kept_out": lambda p, window, keep: p - keep,
+         "far": lambda p, window, keep: p - p // 3}
+LENGTHS = [230, 70, 1, 131]
+
+
+def planted_pages(rng, T, H, G, d, vd, window, keep, where):
+    """Sequences of LENGTHS tokens with planted keys, written into pages in no particular order."""
+    import torch
+    seqs = plant_attention(rng, LENGTHS, H, G, d, vd, window, keep, lambda p: WHERE[where](p, window, keep), 6.0)
+    n_pages = sum(-(-n // PAGE) for n in LENGTHS)
+    order = rng.permutation(n_pages)
+    k_pages = torch.zeros((n_pages + 1, G, PAGE, d), dtype=T, device="cuda")
+    v_pages = torch.zeros((n_pages + 1, G, PAGE, vd), dtype=T, device="cuda")
+    table = np.full((len(LENGTHS), 4), -1, dtype=np.int32)
+    at = 0
+    for s, (n, (q, k, v)) in enumerate(zip(LENGTHS, seqs)):
+        for pg in range(-(-n // PAGE)):
+            page, rows = int(order[at]), slice(pg * PAGE, min(n, (pg + 1) * PAGE))
+            at += 1
+            table[s, pg] = page
+            k_pages[page, :, :rows.stop - rows.start] = dev(k[rows], T).transpose(0, 1)
+            v_pages[page, :, :rows.stop - rows.start] = dev(v[rows], T).transpose(0, 1)
+    return seqs, k_pages, v_pages, table
+
+
+def without_unseen_pages(table, take, window, keep):
+    """The page table as the cache leaves it: pages that hold no key any of the queries `take` can see are given back."""
+    gone = table.copy()
+    for s, n in enumerate(LENGTHS):
+        first_query = min(p for t, ps in take if t == s for p in ps)
+        for pg in range(-(-n // PAGE)):
+            if pg * PAGE >= keep and (pg + 1) * PAGE <= first_query - window + 1:
+                gone[s, pg] = -1
+    return gone
+
+
+def check_planted(got, take, seqs, T, window, keep, where, tol):
+    row = 0
+    for s, ps in take:
+        q, k, v = (f64(dev(a, T)) for a in seqs[s])
+        want = plain.softmax_attention(q, k, v, 0.5, plain.visible(LENGTHS[s], window, keep))
+        for p in ps:
+            assert np.allclose(got[row], want[p], atol=tol), (s, p, where)
+            row += 1
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,G,d,vd,window,keep", [(4, 2, 16, 24, 40, 6), (2, 1, 64, 64, 70, 70), (3, 3, 5, 9, 1, 2), (2, 2, 32, 32, 64, 0),
                                                   (4, 1, 64, 64, 130, 1), (1, 1, 8, 8, 200, 65)])
-@pytest.mark.parametrize("where", ["edge_in", "edge_out", "kept_in", "kept_out", "far"])
+@pytest.mark.parametrize("where", sorted(WHERE))
 def test_attention_sees_the_window_and_the_kept_keys_and_nothing_between(dtype, H, G, d, vd, window, keep, where):
     """The general attention kernel over pages, with one key made to stand out: just inside the window's edge, just
     outside, the last kept key, the first key after the kept ones, and a key far back; over page borders, for prompts, for
@@ -306,47 +353,53 @@ def test_attention_sees_the_window_and_the_kept_keys_and_nothing_between(dtype, 
     from qwen3_b200.csrc import ops
     rng = np.random.default_rng(d * 100 + window)
     T = torch_dtype(dtype)
-    back = {"edge_in": lambda p: window - 1, "edge_out": lambda p: window, "kept_in": lambda p: p - (keep - 1),
-            "kept_out": lambda p: p - keep, "far": lambda p: p - p // 3}[where]
-    lengths = [230, 70, 1, 131]
-    seqs = plant_attention(rng, lengths, H, G, d, vd, window, keep, back, 6.0)
-    n_pages = sum(-(-n // PAGE) for n in lengths)
-    order = rng.permutation(n_pages)                               # pages in no particular order
-    k_pages = torch.zeros((n_pages + 1, G, PAGE, d), dtype=T, device="cuda")
-    v_pages = torch.zeros((n_pages + 1, G, PAGE, vd), dtype=T, device="cuda")
-    table = np.full((len(lengths), 4), -1, dtype=np.int32)
-    at = 0
-    for s, (n, (q, k, v)) in enumerate(zip(lengths, seqs)):
-        for pg in range(-(-n // PAGE)):
-            page, rows = int(order[at]), slice(pg * PAGE, min(n, (pg + 1) * PAGE))
-            at += 1
-            table[s, pg] = page
-            k_pages[page, :, :rows.stop - rows.start] = dev(k[rows], T).transpose(0, 1)
-            v_pages[page, :, :rows.stop - rows.start] = dev(v[rows], T).transpose(0, 1)
+    seqs, k_pages, v_pages, table = planted_pages(rng, T, H, G, d, vd, window, keep, where)
     # the queries: every position of sequence 0, the last 30 of sequence 1 (a portion), the last position of 2 and 3
-    take = [(0, list(range(lengths[0]))), (1, list(range(40, 70))), (2, [0]), (3, [130])]
+    take = [(0, list(range(LENGTHS[0]))), (1, list(range(40, 70))), (2, [0]), (3, [130])]
     qs = np.concatenate([seqs[s][0][p] for s, p in take])
     seq = np.concatenate([np.full(len(p), s) for s, p in take]).astype(np.int32)
     pos = np.concatenate([p for _, p in take]).astype(np.int32)
     N = len(pos)
-    # pages that hold no visible key are gone (as the cache gives them back): the kernel may not touch them
-    gone = table.copy()
-    for s, n in enumerate(lengths):
-        first_query = min(p for t, ps in take if t == s for p in ps)
-        for pg in range(-(-n // PAGE)):
-            if pg * PAGE >= keep and (pg + 1) * PAGE <= first_query - window + 1:
-                gone[s, pg] = -1
+    gone = without_unseen_pages(table, take, window, keep)
     out = torch.empty((N, H * vd), dtype=T, device="cuda")
     ops.attention_generic(dev(qs.reshape(N, H * d), T), k_pages, v_pages, out, dev(seq, torch.int32), dev(pos, torch.int32),
                           dev(gone, torch.int32), N, H, G, d, 0.5, window=window, value_dim=vd, keep_first=keep)
-    got = f64(out).reshape(N, H, vd)
-    row = 0
-    for s, ps in take:
-        q, k, v = (f64(dev(a, T)) for a in seqs[s])
-        want = plain.softmax_attention(q, k, v, 0.5, plain.visible(lengths[s], window, keep))
-        for p in ps:
-            assert np.allclose(got[row], want[p], atol=2e-5 if dtype == "float32" else 3e-2), (s, p, where)
-            row += 1
+    check_planted(f64(out).reshape(N, H, vd), take, seqs, T, window, keep, where, 2e-5 if dtype == "float32" else 3e-2)
+
+
+@pytest.mark.parametrize("H,G,d,vd,window,keep", [(4, 2, 16, 32, 40, 6), (2, 1, 64, 64, 70, 70), (2, 2, 32, 32, 64, 0), (4, 1, 64, 64, 130, 1),
+                                                  (2, 1, 128, 64, 200, 65), (16, 1, 16, 16, 1, 2), (2, 2, 64, 64, 63, 129)])
+@pytest.mark.parametrize("where", sorted(WHERE))
+def test_tiled_attention_kernels_walk_the_kept_pages_before_the_window_s(H, G, d, vd, window, keep, where):
+    """The same through the tensor-core kernels of the bfloat16 path: prompts and portions in tiles of 64 rows, single
+    tokens with the pages split over several blocks (1, 2 and 5 of them)."""
+    import torch
+    from qwen3_b200.csrc import ops
+    rng = np.random.default_rng(d * 100 + window + 1)
+    T = torch.bfloat16
+    seqs, k_pages, v_pages, table = planted_pages(rng, T, H, G, d, vd, window, keep, where)
+    take = [(0, list(range(LENGTHS[0]))), (1, list(range(40, 70))), (2, [0]), (3, [130])]
+    qs = np.concatenate([seqs[s][0][p] for s, p in take])
+    N = len(qs)
+    start = np.concatenate([[0], np.cumsum([len(p) for _, p in take])]).astype(np.int32)
+    pos0 = np.array([p[0] for _, p in take], dtype=np.int32)
+    gone = without_unseen_pages(table, take, window, keep)
+    out = torch.empty((N, H * vd), dtype=T, device="cuda")
+    ops.attention_capped_prefill(dev(qs.reshape(N, H * d), T), k_pages, v_pages, out, dev(start, torch.int32), dev(pos0, torch.int32),
+                                 dev(gone, torch.int32), len(take), LENGTHS[0], H, G, d, vd, 0.5, 0.0, None, False, window=window,
+                                 keep_first=keep)
+    check_planted(f64(out).reshape(N, H, vd), take, seqs, T, window, keep, where, 3e-2)
+    last = [(s, [n - 1]) for s, n in enumerate(LENGTHS)]
+    ql = np.concatenate([seqs[s][0][p] for s, p in last])
+    gone = without_unseen_pages(table, last, window, keep)
+    for splits in (1, 2, 5):
+        scratch = torch.empty(len(last) * H * splits * (vd + 2), dtype=torch.float32, device="cuda")
+        out = torch.empty((len(last), H * vd), dtype=T, device="cuda")
+        ops.attention_capped_decode(dev(ql.reshape(len(last), H * d), T), k_pages, v_pages, out, scratch,
+                                    dev(np.arange(len(last)), torch.int32), dev([n - 1 for n in LENGTHS], torch.int32),
+                                    dev(gone, torch.int32), len(last), H, G, d, vd, 0.5, 0.0, None, False, splits, window=window,
+                                    keep_first=keep)
+        check_planted(f64(out).reshape(len(last), H, vd), last, seqs, T, window, keep, where, 3e-2)
 
 
 # ============================================================================ the engine
