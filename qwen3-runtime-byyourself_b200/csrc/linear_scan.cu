@@ -5,8 +5,8 @@
 //
 // in two forms that share one kernel:
 //
-//   per channel  : a_t = sigmoid(z_t + bias)^(1/tau), one decay per key channel from 32-bit logits z [N, H*d]; b = 1
-//                  (gated linear attention).
+//   per channel  : a_t [N, H*d] (float32), one decay per key channel, b = 1 (gated linear attention; `channel_decay`
+//                  makes a_t = sigmoid(z_t + bias)^(1/tau) from 32-bit logits, once for all the blocks that read it).
 //   per head     : a_t = keep[t, h], b_t = write[t, h], two 32-bit numbers per token and head that `memory_gates`
 //                  prepares (a matrix memory with exponential gates).  With `ones` the state has one column more than
 //                  the values, vdx = vd + 1, whose value is 1 for every token: that column is the normaliser
@@ -21,9 +21,9 @@
 //                  depends on the sizes only, never on the step: a token's output is the same bits however the
 //                  sequence was cut.  A decode step is the same kernel with one token.
 //   memory_gates : for every (sequence, head) one warp turns the gate logits zi, zf [N, H] (float32, biases added here)
-//                  into i = cap tanh(zi / cap), f = logsigmoid(cap tanh(zf / cap)), walks the running maximum
-//                  m_t = max(f_t + m_(t-1), i_t) from the slot's stored m (0 for a new sequence) in token order, and
-//                  writes keep = exp(f + m_(t-1) - m_t), write = exp(i - m_t) and low = exp(-m_t).
+//                  into i = cap tanh(zi / cap), f = logsigmoid(cap tanh(zf / cap)), finds the running maximum
+//                  m_t = max(f_t + m_(t-1), i_t) from the slot's stored m (0 for a new sequence), 32 tokens at a time by a
+//                  scan over the warp, and writes keep = exp(f + m_(t-1) - m_t), write = exp(i - m_t) and low = exp(-m_t).
 //   head_gated_norm : per (token, head): x = o (divided by max(|n . q|, low) + floor if the state has the normaliser
 //                  column), y = x / sqrt(mean(x^2) + eps) * w * act(gate), act = sigmoid or SiLU; w one vector per
 //                  head or one for all heads.
@@ -46,9 +46,7 @@ struct ScanArgs {
     const void* k;
     const void* v;
     int64_t row;
-    const float* z;                // per channel: [N, H * d] decay logits; per head: null
-    const float* z_bias;           // [H * d]
-    float inv_tau;
+    const float* z;                // per channel: [N, H * d] decays; per head: null
     const float* keep;             // per head: [N, H]
     const float* write;
     float q_scale;
@@ -82,12 +80,10 @@ decay_scan_kernel(const ScanArgs p, int R, int vt, int stage) {
     // which values of a stage this thread fetches: x = tid + n * nthreads < stage * d (q, k, decay), < stage * vt (v);
     // the token and the channel of each, found once (token << 16 | channel; a token beyond the stage: none)
     int at_qk[PRE_QK], at_v[PRE_V];
-    float bias_r[PRE_QK];
 #pragma unroll
     for (int n = 0; n < PRE_QK; ++n) {
         const int x = tid + n * nthreads;
         at_qk[n] = x < stage * d ? (x / d) << 16 | (x % d) : MAX_STAGE << 16;
-        bias_r[n] = PER_CHANNEL && x < stage * d && p.z_bias != nullptr ? p.z_bias[head * d + x % d] : 0.0f;
     }
 #pragma unroll
     for (int n = 0; n < PRE_V; ++n) {
@@ -137,7 +133,7 @@ decay_scan_kernel(const ScanArgs p, int R, int vt, int stage) {
             if (tt < n_stage) {
                 q_s[tt * dp + i] = to_f32<T>(q_raw[n]) * p.q_scale;
                 k_s[tt * dp + i] = to_f32<T>(k_raw[n]);
-                if constexpr (PER_CHANNEL) a_s[tt * dp + i] = expf(log_sigmoid(z_raw[n] + bias_r[n]) * p.inv_tau);
+                if constexpr (PER_CHANNEL) a_s[tt * dp + i] = z_raw[n];
             }
         }
 #pragma unroll
@@ -244,8 +240,16 @@ int decay_scan_launch(const ScanArgs& p, int n_seqs, cudaStream_t stream) {
 #undef Q3_SCAN
 }
 
-// One warp per (sequence, head); 32 tokens at a time: the gates' activations side by side, the running maximum
-// lane after lane, the exponentials side by side again.
+// a = sigmoid(z + bias)^(1 / tau) = exp(logsigmoid(z + bias) / tau), in place.
+__global__ void channel_decay_kernel(float* __restrict__ z, const float* __restrict__ bias, float inv_tau, int64_t n, int width) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        z[i] = expf(log_sigmoid(z[i] + (bias != nullptr ? bias[i % width] : 0.0f)) * inv_tau);
+}
+
+// One warp per (sequence, head); 32 tokens at a time: the gates' activations side by side, the running maximum by a
+// scan over the lanes, the exponentials side by side again.
 __global__ void memory_gates_kernel(const float* __restrict__ zi, const float* __restrict__ zf, const float* __restrict__ bias_i,
                                     const float* __restrict__ bias_f, float cap, float* __restrict__ m_state, int64_t slot_stride,
                                     const int* __restrict__ seq_start, const int* __restrict__ seq_slots, float* __restrict__ keep,
@@ -266,16 +270,23 @@ __global__ void memory_gates_kernel(const float* __restrict__ zi, const float* _
             gi = cap * tanhf((zi[(int64_t)t * z_row + head] + bi) * inv_cap);
             gf = log_sigmoid(cap * tanhf((zf[(int64_t)t * z_row + head] + bf) * inv_cap));
         }
-        float m_before = 0.0f, m_mine = 0.0f;
-        for (int s = 0; s < n; ++s) {
-            const float f_s = __shfl_sync(0xffffffffu, gf, s), i_s = __shfl_sync(0xffffffffu, gi, s);
-            const float m_new = fmaxf(f_s + m, i_s);
-            if (lane == s) {
-                m_before = m;
-                m_mine = m_new;
+        // m_t = max(f_t + m_(t-1), i_t) is the map m -> max(m + F, I) with (F, I) = (f_t, i_t); two such maps in a row
+        // are one, (F1, I1) then (F2, I2) = (F1 + F2, max(I1 + F2, I2)): a scan over the warp gives every lane the map of
+        // all tokens up to its own.  (The maximum only has to be the same number wherever it is used: keep, write and
+        // low are made from the m computed here, so the order of these sums shows in no output beyond rounding.)
+        float F = t < t_end ? gf : 0.0f, I = t < t_end ? gi : -INFINITY;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const float Fp = __shfl_up_sync(0xffffffffu, F, off), Ip = __shfl_up_sync(0xffffffffu, I, off);
+            if (lane >= off) {
+                I = fmaxf(Ip + F, I);
+                F = Fp + F;
             }
-            m = m_new;
         }
+        const float m_mine = fmaxf(m + F, I);
+        float m_before = __shfl_up_sync(0xffffffffu, m_mine, 1);
+        if (lane == 0) m_before = m;
+        m = __shfl_sync(0xffffffffu, m_mine, n - 1);
         if (t < t_end) {
             keep[(int64_t)t * H + head] = expf(gf + m_before - m_mine);
             write[(int64_t)t * H + head] = expf(gi - m_mine);
@@ -319,12 +330,12 @@ __global__ void head_gated_norm_kernel(const float* __restrict__ o, const float*
 
 #define Q3_SCAN_EXPORTS(SUFFIX, T)                                                                                           \
     Q3_EXPORT int q3_decay_scan_##SUFFIX(const void* q, const void* k, const void* v, int64_t row, const float* z,          \
-                                         const float* z_bias, float inv_tau, const float* keep, const float* write,         \
+                                         const float* keep, const float* write,                                             \
                                          float q_scale, int ones, float* state, int64_t slot_stride, const int* seq_start,  \
                                          const int* seq_slots, float* out, int n_seqs, int heads, int d, int vd,           \
                                          void* stream) {                                                                   \
         ScanArgs p;                                                                                                         \
-        p.q = q; p.k = k; p.v = v; p.row = row; p.z = z; p.z_bias = z_bias; p.inv_tau = inv_tau; p.keep = keep;             \
+        p.q = q; p.k = k; p.v = v; p.row = row; p.z = z; p.keep = keep;                                                     \
         p.write = write; p.q_scale = q_scale; p.ones = ones; p.state = state; p.slot_stride = slot_stride;                  \
         p.seq_start = seq_start; p.seq_slots = seq_slots; p.out = out; p.H = heads; p.d = d; p.vd = vd;                     \
         p.vdx = vd + (ones ? 1 : 0);                                                                                        \
@@ -346,6 +357,14 @@ __global__ void head_gated_norm_kernel(const float* __restrict__ o, const float*
 
 Q3_SCAN_EXPORTS(f32, float)
 Q3_SCAN_EXPORTS(bf16, bf16)
+
+Q3_EXPORT int q3_channel_decay(float* z, const float* bias, float inv_tau, int64_t n_tokens, int width, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (width <= 0) return Q3_ERR_BAD_SIZE;
+    const int64_t n = n_tokens * width, blocks = (n + 255) / 256;
+    return (int)q3_launch(channel_decay_kernel, dim3((unsigned)(blocks < 65536 ? blocks : 65536)), dim3(256), 0, (cudaStream_t)stream, z,
+                          bias, inv_tau, n, width);
+}
 
 Q3_EXPORT int q3_memory_gates(const float* zi, const float* zf, const float* bias_i, const float* bias_f, float cap,
                               float* m_state, int64_t slot_stride, const int* seq_start, const int* seq_slots, float* keep,

@@ -622,28 +622,36 @@ def _scan_views(q, k, v, state, out, heads, d, vd, vdx):
 
 
 def decay_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, seq_start: torch.Tensor, seq_slots: torch.Tensor,
-               out: torch.Tensor, n_seqs: int, heads: int, d: int, vd: int, q_scale: float = 1.0, z: Optional[torch.Tensor] = None,
-               z_bias: Optional[torch.Tensor] = None, tau: float = 1.0, keep: Optional[torch.Tensor] = None,
-               write: Optional[torch.Tensor] = None, ones: bool = False) -> torch.Tensor:
+               out: torch.Tensor, n_seqs: int, heads: int, d: int, vd: int, q_scale: float = 1.0, decay: Optional[torch.Tensor] = None,
+               keep: Optional[torch.Tensor] = None, write: Optional[torch.Tensor] = None, ones: bool = False) -> torch.Tensor:
     """S_t = diag(a_t) S_(t-1) + k_t (b_t v_t)^T, o_t = S_t^T (q_t * q_scale) over the new tokens of every sequence, from and to
     the state rows (`state`: a view [slots, heads * d * vdx] of float32 rows).  q, k, v: column views of one projection
-    output (same row stride).  With `z` [N, heads * d] (float32 logits): a = sigmoid(z + z_bias)^(1 / tau) per channel,
-    b = 1.  With `keep`, `write` [N, heads] (float32): a and b per head.  `ones`: vdx = vd + 1, the state's last column takes
+    output (same row stride).  With `decay` [N, heads * d] (float32, see `channel_decay`): a per channel, b = 1.  With
+    `keep`, `write` [N, heads] (float32): a and b per head.  `ones`: vdx = vd + 1, the state's last column takes
     the value 1 (a normaliser); else vdx = vd.  out [N, heads * vdx] float32."""
     vdx = vd + (1 if ones else 0)
     row = _scan_views(q, k, v, state, out, heads, d, vd, vdx)
     N = q.shape[0]
+    z = decay
     if (z is None) == (keep is None) or (z is not None and (tuple(z.shape) != (N, heads * d) or not z.is_contiguous())) \
             or (keep is not None and (write is None or keep.numel() < N * heads or write.numel() < N * heads)):
-        raise KernelError("decay_scan: a decay per channel (z) or gates per head (keep, write)")
+        raise KernelError("decay_scan: a decay per channel or gates per head (keep, write)")
     fn = _fn("linear_scan.cu", f"q3_decay_scan_{_suffix(q)}",
-             [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_float, c_int, c_void_p, c_int64,
+             [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_int64,
               c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    _check(fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), row, _ptr(z, "z", torch.float32), _ptr(z_bias, "z_bias", torch.float32),
-              1.0 / float(tau), _ptr(keep, "keep", torch.float32), _ptr(write, "write", torch.float32), float(q_scale), int(bool(ones)),
+    _check(fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), row, _ptr(z, "decay", torch.float32), _ptr(keep, "keep", torch.float32), _ptr(write, "write", torch.float32), float(q_scale), int(bool(ones)),
               state.data_ptr(), state.stride(0), _dev(seq_start, "seq_start", torch.int32), _dev(seq_slots, "seq_slots", torch.int32),
               _dev(out, "out"), int(n_seqs), heads, d, vd, _stream()), "decay_scan")
     return out
+
+
+def channel_decay(z: torch.Tensor, bias: Optional[torch.Tensor], tau: float) -> torch.Tensor:
+    """In place: z <- sigmoid(z + bias)^(1 / tau); z [N, width] float32 logits, bias float32 [width] or None."""
+    if z.dtype != torch.float32 or z.dim() != 2 or (bias is not None and bias.numel() != z.shape[1]) or not tau > 0:
+        raise KernelError("channel_decay: float32 logits [N, width], one bias per column, a positive tau")
+    fn = _fn("linear_scan.cu", "q3_channel_decay", [c_void_p, c_void_p, c_float, c_int64, c_int, c_void_p])
+    _check(fn(_dev(z, "z"), _ptr(bias, "bias", torch.float32), 1.0 / float(tau), z.shape[0], z.shape[1], _stream()), "channel_decay")
+    return z
 
 
 def memory_gates(z: torch.Tensor, bias_i: torch.Tensor, bias_f: torch.Tensor, cap: float, m_state: torch.Tensor, seq_start, seq_slots,

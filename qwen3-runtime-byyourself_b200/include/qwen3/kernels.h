@@ -351,12 +351,14 @@ int q3_short_conv_bf16(const void* u, int64_t row_in, const float* w, float* sta
                        void* stream);
 
 /* ---- linear_scan.cu: linear attention with keys ------------------------------------------------------------- */
-/* S_t = diag(a_t) S_(t-1) + k_t (b_t v_t)^T, o_t = S_t^T (q_t q_scale); z given: a = sigmoid(z + z_bias)^inv_tau per channel,
-   b = 1; keep and write given: a and b per (token, head); ones: the state has a last column whose value is 1 */
-int q3_decay_scan_f32(const void* q, const void* k, const void* v, int64_t row, const float* z, const float* z_bias, float inv_tau,
+/* z <- sigmoid(z + bias)^inv_tau in place: the decays per key channel from their logits [n_tokens, width] */
+int q3_channel_decay(float* z, const float* bias, float inv_tau, int64_t n_tokens, int width, void* stream);
+/* S_t = diag(a_t) S_(t-1) + k_t (b_t v_t)^T, o_t = S_t^T (q_t q_scale); z given: the decays a per (token, channel), b = 1;
+   keep and write given: a and b per (token, head); ones: the state has a last column whose value is 1 */
+int q3_decay_scan_f32(const void* q, const void* k, const void* v, int64_t row, const float* z,
                       const float* keep, const float* write, float q_scale, int ones, float* state, int64_t slot_stride,
                       const int* seq_start, const int* seq_slots, float* out, int n_seqs, int heads, int d, int vd, void* stream);
-int q3_decay_scan_bf16(const void* q, const void* k, const void* v, int64_t row, const float* z, const float* z_bias, float inv_tau,
+int q3_decay_scan_bf16(const void* q, const void* k, const void* v, int64_t row, const float* z,
                        const float* keep, const float* write, float q_scale, int ones, float* state, int64_t slot_stride,
                        const int* seq_start, const int* seq_slots, float* out, int n_seqs, int heads, int d, int vd, void* stream);
 /* i = cap tanh((zi + bias_i) / cap), f = logsigmoid(cap tanh((zf + bias_f) / cap)), m_t = max(f_t + m_(t-1), i_t) from and to

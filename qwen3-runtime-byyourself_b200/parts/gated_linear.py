@@ -70,10 +70,11 @@ class GatedLinearAttention(Part):
         linear(x, self.w_a1, narrow)
         z = ctx.scratch.get("gla.z", (N, h * d), torch.float32)
         linear(narrow, self.w_a2, z)
+        ops.channel_decay(z, self.decay_bias, self.tau)          # once per token and channel: every block of the scan reads it
         o = ctx.scratch.get("gla.o", (N, h * vd), torch.float32)
         state = cache.state.view(cache.state.shape[0], -1)
         ops.decay_scan(proj[:, :h * d], proj[:, h * d:2 * h * d], proj[:, 2 * h * d:2 * h * d + h * vd], state, ctx.seq_start,
-                       ctx.seq_slots, o, ctx.n_seqs, h, d, vd, q_scale=d ** -0.5, z=z, z_bias=self.decay_bias, tau=self.tau)
+                       ctx.seq_slots, o, ctx.n_seqs, h, d, vd, q_scale=d ** -0.5, decay=z)
         gated = ctx.scratch.get("gla.gated", (N, h * vd), ctx.dtype)
         ops.head_gated_norm(o, self.norm_weight, proj[:, 2 * h * d + h * vd:], self.eps, gated, h, vd, act="silu")
         out = ctx.scratch.get(self.out_name, (N, self.hidden_size), ctx.dtype)

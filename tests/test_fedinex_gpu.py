@@ -80,7 +80,8 @@ def test_decay_scan_over_unequal_sequences_and_from_its_state(dtype, per_channel
         write = dev(rng.uniform(0.0, 1.5, (N, heads)), torch.float32)
         out = torch.full((N, heads * vdx), 9.0, dtype=torch.float32, device="cuda")
         qv, kv, vv = proj[:, :heads * d], proj[:, heads * d:2 * heads * d], proj[:, 2 * heads * d:2 * heads * d + heads * vd]
-        kw = dict(z=z, z_bias=dev(bias, torch.float32), tau=tau) if per_channel else dict(keep=keep, write=write, ones=True)
+        logits = f64(z)
+        kw = dict(decay=ops.channel_decay(z, dev(bias, torch.float32), tau)) if per_channel else dict(keep=keep, write=write, ones=True)
         ops.decay_scan(qv, kv, vv, state, dev(start, torch.int32), dev([s for s, _ in live], torch.int32), out, len(live), heads, d, vd,
                        q_scale=scale, **kw)
         got = f64(out).reshape(N, heads, vdx)
@@ -92,7 +93,7 @@ def test_decay_scan_over_unequal_sequences_and_from_its_state(dtype, per_channel
                 k = pd[rows, (heads + h) * d:(heads + h + 1) * d]
                 v = pd[rows, 2 * heads * d + h * vd:2 * heads * d + (h + 1) * vd]
                 if per_channel:
-                    a = plain.sigmoid(f64(z)[rows, h * d:(h + 1) * d] + bias[h * d:(h + 1) * d]) ** (1.0 / tau)
+                    a = plain.sigmoid(logits[rows, h * d:(h + 1) * d] + bias[h * d:(h + 1) * d]) ** (1.0 / tau)
                     b = np.ones(n)
                 else:
                     a = np.repeat(f64(keep)[rows, h][:, None], d, axis=1)
@@ -130,12 +131,12 @@ def test_memory_gates_walk_the_running_maximum_from_zero_and_across_steps(heads)
         for i, (slot, n) in enumerate(live):
             for t in range(start[i], start[i + 1]):
                 m_new = np.maximum(gf[t] + m[slot], gi[t])
-                assert np.allclose(f64(keep)[t], np.exp(gf[t] + m[slot] - m_new), rtol=1e-5, atol=1e-7)
-                assert np.allclose(f64(write)[t], np.exp(gi[t] - m_new), rtol=1e-5, atol=1e-7)
-                assert np.allclose(f64(low)[t], np.exp(-m_new), rtol=1e-5, atol=1e-7)
+                assert np.allclose(f64(keep)[t], np.exp(gf[t] + m[slot] - m_new), rtol=1e-4, atol=1e-7)
+                assert np.allclose(f64(write)[t], np.exp(gi[t] - m_new), rtol=1e-4, atol=1e-7)
+                assert np.allclose(f64(low)[t], np.exp(-m_new), rtol=1e-4, atol=1e-7)
                 m[slot] = m_new
     for slot in slots:
-        assert np.allclose(f64(m_state)[slot], m[slot], rtol=1e-6, atol=1e-6)
+        assert np.allclose(f64(m_state)[slot], m[slot], rtol=1e-5, atol=1e-5)
     assert np.all(f64(whole)[:, :2] == 0.0) and np.all(f64(whole)[1] == 0.0)
 
 
