@@ -17,7 +17,9 @@
 //                  thread (j, r) owns column j of the tile and the rows r * ROWS .. r * ROWS + ROWS - 1; the threads of
 //                  a column add their partial outputs through shared memory.  It reads the state from the slot's row
 //                  before the first token and writes it back after the last.  Tokens arrive a stage (up to 16) at a
-//                  time: while a stage is walked, the rows of the next are on their way into registers.  The launch
+//                  time: while a stage is walked, the rows of the next are on their way into registers, the decays of
+//                  the one after it too, and the lines of q, k and v of the one after it are asked into L2 (a walk of
+//                  16 tokens is about as long as a trip to DRAM and hides no more than that).  The launch
 //                  depends on the sizes only, never on the step: a token's output is the same bits however the
 //                  sequence was cut.  A decode step is the same kernel with one token.
 //   memory_gates : for every (sequence, head) one warp turns the gate logits zi, zf [N, H] (float32, biases added here)
@@ -39,6 +41,9 @@ constexpr int MAX_STAGE = 16;     // tokens fetched together
 constexpr int PRE_QK = 8;         // values of q, of k and of the decay logits that a thread holds for the next stage
 constexpr int PRE_V = 2;          // values of v
 
+// Asks for a line to be brought into L2; nothing waits for it.
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.0f) - log1pf(expf(-fabsf(z))); }
 
 struct ScanArgs {
@@ -59,8 +64,10 @@ struct ScanArgs {
     int H, d, vd, vdx;
 };
 
-template <typename T, int ROWS, bool PER_CHANNEL>
-__global__ void __launch_bounds__(512)
+// MAXT: the most threads a block has (256 for keys up to 128 wide, which leaves a thread room for the values it holds for
+// the stages to come)
+template <typename T, int ROWS, bool PER_CHANNEL, int MAXT>
+__global__ void __launch_bounds__(MAXT)
 decay_scan_kernel(const ScanArgs p, int R, int vt, int stage) {
     extern __shared__ __align__(16) float smem[];
     const int dp = R * ROWS;                 // d rounded up to whole threads: the rows beyond d hold q = k = 0
@@ -74,9 +81,13 @@ decay_scan_kernel(const ScanArgs p, int R, int vt, int stage) {
     const int head = blockIdx.x, seq = blockIdx.y, col0 = blockIdx.z * vt;
     const int tid = threadIdx.x, nthreads = blockDim.x, jt = tid % vt, j = col0 + jt, r = tid / vt;
     const bool live = r < R && j < vdx;
-    const T* q_g = reinterpret_cast<const T*>(p.q) + (int64_t)head * d;
-    const T* k_g = reinterpret_cast<const T*>(p.k) + (int64_t)head * d;
-    const T* v_g = reinterpret_cast<const T*>(p.v) + (int64_t)head * vd;
+    // nothing this kernel writes is read by it again: the inputs go through the read-only path
+    const T* __restrict__ q_g = reinterpret_cast<const T*>(p.q) + (int64_t)head * d;
+    const T* __restrict__ k_g = reinterpret_cast<const T*>(p.k) + (int64_t)head * d;
+    const T* __restrict__ v_g = reinterpret_cast<const T*>(p.v) + (int64_t)head * vd;
+    const float* __restrict__ z_g = p.z, * __restrict__ keep_g = p.keep, * __restrict__ write_g = p.write;
+    float* __restrict__ out_g = p.out;
+    const int64_t row_g = p.row;
     // which values of a stage this thread fetches: x = tid + n * nthreads < stage * d (q, k, decay), < stage * vt (v);
     // the token and the channel of each, found once (token << 16 | channel; a token beyond the stage: none)
     int at_qk[PRE_QK], at_v[PRE_V];
@@ -101,28 +112,62 @@ decay_scan_kernel(const ScanArgs p, int R, int vt, int stage) {
     }
     const int t_begin = p.seq_start[seq], t_end = p.seq_start[seq + 1];
     T q_raw[PRE_QK], k_raw[PRE_QK], v_raw[PRE_V];
-    float z_raw[PER_CHANNEL ? PRE_QK : 1], keep_raw = 0.0f, write_raw = 1.0f;
+    float z_raw[PER_CHANNEL ? PRE_QK : 1], z_ahead[PER_CHANNEL ? PRE_QK : 1], keep_raw = 0.0f, write_raw = 1.0f;
+    // the decays are twice as many bytes as q or k, and asking them into L2 ahead did not hide them: they are loaded into
+    // registers a stage earlier than the rest, two stages before they are walked
+    auto load_decays = [&](int t0) {
+        if constexpr (PER_CHANNEL) {
+            const int n_stage = min(stage, t_end - t0);
+#pragma unroll
+            for (int n = 0; n < PRE_QK; ++n) {
+                const int tt = at_qk[n] >> 16, i = at_qk[n] & 0xffff;
+                if (tt < n_stage) z_ahead[n] = __ldg(z_g + ((int64_t)(t0 + tt) * H + head) * d + i);
+            }
+        }
+    };
     auto fetch = [&](int t0) {
         const int n_stage = min(stage, t_end - t0);
+        if constexpr (PER_CHANNEL) {
+#pragma unroll
+            for (int n = 0; n < PRE_QK; ++n) z_raw[n] = z_ahead[n];
+            load_decays(t0 + stage);
+        }
 #pragma unroll
         for (int n = 0; n < PRE_QK; ++n) {
             const int tt = at_qk[n] >> 16, i = at_qk[n] & 0xffff;
             if (tt < n_stage) {
-                q_raw[n] = q_g[(int64_t)(t0 + tt) * p.row + i];
-                k_raw[n] = k_g[(int64_t)(t0 + tt) * p.row + i];
-                if constexpr (PER_CHANNEL) z_raw[n] = p.z[((int64_t)(t0 + tt) * H + head) * d + i];
+                q_raw[n] = __ldg(q_g + (int64_t)(t0 + tt) * row_g + i);
+                k_raw[n] = __ldg(k_g + (int64_t)(t0 + tt) * row_g + i);
             }
         }
 #pragma unroll
         for (int n = 0; n < PRE_V; ++n) {
             const int tt = at_v[n] >> 16, c = at_v[n] & 0xffff;
-            if (tt < n_stage && col0 + c < vd) v_raw[n] = v_g[(int64_t)(t0 + tt) * p.row + col0 + c];
+            if (tt < n_stage && col0 + c < vd) v_raw[n] = __ldg(v_g + (int64_t)(t0 + tt) * row_g + col0 + c);
         }
         if constexpr (!PER_CHANNEL) {
             if (tid < n_stage) {
-                keep_raw = p.keep[(int64_t)(t0 + tid) * H + head];
-                write_raw = p.write[(int64_t)(t0 + tid) * H + head];
+                keep_raw = __ldg(keep_g + (int64_t)(t0 + tid) * H + head);
+                write_raw = __ldg(write_g + (int64_t)(t0 + tid) * H + head);
             }
+        }
+        // the stage after that one: its lines are asked into L2 now (one request per 32 bytes), so that its loads, a stage
+        // from now, find them there - a walk of 16 tokens is about as long as a trip to DRAM and hides no more
+        const int n_ahead = min(stage, t_end - t0 - stage);
+#pragma unroll
+        for (int n = 0; n < PRE_QK; ++n) {
+            const int tt = at_qk[n] >> 16, i = at_qk[n] & 0xffff;
+            if (tt < n_ahead && (i & 7) == 0) {
+                if ((i & 15) == 0 || sizeof(T) == 4) {
+                    prefetch_l2(q_g + (int64_t)(t0 + stage + tt) * row_g + i);
+                    prefetch_l2(k_g + (int64_t)(t0 + stage + tt) * row_g + i);
+                }
+            }
+        }
+#pragma unroll
+        for (int n = 0; n < PRE_V; ++n) {
+            const int tt = at_v[n] >> 16, c = at_v[n] & 0xffff;
+            if (tt < n_ahead && c == 0) prefetch_l2(v_g + (int64_t)(t0 + stage + tt) * row_g + col0);
         }
     };
     auto activate = [&](int t0) {
@@ -148,7 +193,10 @@ decay_scan_kernel(const ScanArgs p, int R, int vt, int stage) {
             }
         }
     };
-    if (t_begin < t_end) fetch(t_begin);
+    if (t_begin < t_end) {
+        load_decays(t_begin);
+        fetch(t_begin);
+    }
     __syncthreads();                                     // the zeros are in place
     if (t_begin < t_end) activate(t_begin);
     __syncthreads();
@@ -195,7 +243,7 @@ decay_scan_kernel(const ScanArgs p, int R, int vt, int stage) {
             if (col0 + c < vdx) {
                 float o = 0.0f;
                 for (int rr = 0; rr < R; ++rr) o += red[(tt * R + rr) * vt + c];
-                p.out[((int64_t)(t0 + tt) * H + head) * vdx + col0 + c] = o;
+                out_g[((int64_t)(t0 + tt) * H + head) * vdx + col0 + c] = o;
             }
         }
         if (t0 + stage < t_end) activate(t0 + stage);    // everybody has left the stage's q, k, decay and v
@@ -224,19 +272,21 @@ int decay_scan_launch(const ScanArgs& p, int n_seqs, cudaStream_t stream) {
     const int stage = max(1, min(MAX_STAGE, min(PRE_QK * threads / d, PRE_V * threads / vt)));
     const size_t smem = ((size_t)stage * ((PER_CHANNEL ? 3 : 2) * R * rows + vt + R * vt) + (PER_CHANNEL ? 0 : 2 * MAX_STAGE)) * sizeof(float);
     const dim3 grid(p.H, n_seqs, (vdx + vt - 1) / vt);
-#define Q3_SCAN(ROWS)                                                                                                        \
+#define Q3_SCAN(ROWS, MAXT)                                                                                                  \
     do {                                                                                                                     \
         if (smem > 48 * 1024) {                                                                                              \
-            const cudaError_t e = cudaFuncSetAttribute(decay_scan_kernel<T, ROWS, PER_CHANNEL>,                              \
+            const cudaError_t e = cudaFuncSetAttribute(decay_scan_kernel<T, ROWS, PER_CHANNEL, MAXT>,                        \
                                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);              \
             if (e != cudaSuccess) return (int)e;                                                                             \
         }                                                                                                                    \
-        return (int)q3_launch(decay_scan_kernel<T, ROWS, PER_CHANNEL>, grid, dim3(threads), smem, stream, p, R, vt, stage);  \
+        return (int)q3_launch(decay_scan_kernel<T, ROWS, PER_CHANNEL, MAXT>, grid, dim3(threads), smem, stream, p, R, vt,    \
+                              stage);                                                                                        \
     } while (0)
-    if (rows == 1) Q3_SCAN(1);
-    if (rows == 2) Q3_SCAN(2);
-    if (rows == 4) Q3_SCAN(4);
-    Q3_SCAN(8);
+    if (rows == 1) Q3_SCAN(1, 256);                    // d <= 8: at most 128 threads
+    if (rows == 2) Q3_SCAN(2, 256);
+    if (rows == 4) Q3_SCAN(4, 256);
+    if (threads <= 256) Q3_SCAN(8, 256);
+    Q3_SCAN(8, 512);
 #undef Q3_SCAN
 }
 
