@@ -369,36 +369,61 @@ int attention_generic_launch(const T* q, const T* k_pages, const T* v_pages, T* 
 // Values blended across layers, on the value columns of a projection's rows (in place): v <- v + bias first (if
 // any); the first layer of a chain keeps a copy, `first` [N, width]; a later one goes on with
 // v <- (1 - lambda) v + lambda first.  32-bit arithmetic, stored in T.
-template <typename T>
+template <typename T, int VEC>
 __global__ void value_mix_kernel(T* __restrict__ rows, int64_t row, int64_t v_off, int width, const float* __restrict__ bias,
                                  T* __restrict__ first, int save, float lambda, int64_t n_tokens) {
     pdl_launch_dependents();
     pdl_wait();
-    const int64_t total = n_tokens * width;
+    const int per_row = width / VEC;
+    const int64_t total = n_tokens * per_row;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t t = i / width;
-        const int c = (int)(i % width);
+        const int64_t t = i / per_row;
+        const int c = (int)(i % per_row) * VEC;
         T* at = rows + t * row + v_off + c;
-        float v = to_f32<T>(*at);
-        if (bias != nullptr) v = round_to<T>(v + bias[c]);
-        if (save) first[i] = from_f32<T>(v);
-        else v = (1.0f - lambda) * v + lambda * to_f32<T>(first[i]);
-        *at = from_f32<T>(v);
+        float v[VEC], f[VEC];
+        if constexpr (VEC == 1) v[0] = to_f32<T>(*at); else load_pack_f32<T>(at, v);
+        if (bias != nullptr) {
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) v[k] = round_to<T>(v[k] + bias[c + k]);
+        }
+        if (save) {
+            if constexpr (VEC == 1) first[t * width + c] = from_f32<T>(v[0]); else store_pack_f32<T>(first + t * width + c, v);
+        } else {
+            if constexpr (VEC == 1) f[0] = to_f32<T>(first[t * width + c]); else load_pack_f32<T>(first + t * width + c, f);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) v[k] = (1.0f - lambda) * v[k] + lambda * f[k];
+        }
+        if constexpr (VEC == 1) *at = from_f32<T>(v[0]); else store_pack_f32<T>(at, v);
     }
 }
 
 // One sigmoid gate per (token, head) on the attention's output, in place: x[t, h, :] *= sigmoid(gate[t, h]).
-template <typename T>
+template <typename T, int VEC>
 __global__ void head_gate_kernel(T* __restrict__ x, const T* __restrict__ gate, int64_t gate_row, int heads, int vd, int64_t n_tokens) {
     pdl_launch_dependents();
     pdl_wait();
-    const int64_t total = n_tokens * heads * vd;
+    const int per_head = vd / VEC;
+    const int64_t total = n_tokens * heads * per_head;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t th = i / vd, t = th / heads;
+        const int64_t th = i / per_head, t = th / heads;
         const int h = (int)(th % heads);
         const float z = to_f32<T>(gate[t * gate_row + h]);
-        x[i] = from_f32<T>(to_f32<T>(x[i]) / (1.0f + expf(-z)));
+        const float g = 1.0f / (1.0f + expf(-z));
+        T* at = x + i * VEC;
+        float v[VEC];
+        if constexpr (VEC == 1) v[0] = to_f32<T>(*at); else load_pack_f32<T>(at, v);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) v[k] *= g;
+        if constexpr (VEC == 1) *at = from_f32<T>(v[0]); else store_pack_f32<T>(at, v);
     }
+}
+
+template <typename Kernel, typename... Args>
+int launch_flat(Kernel kernel, int64_t work, cudaStream_t stream, Args... args) {
+    int64_t blocks = (work + 255) / 256;
+    const int64_t resident = (int64_t)q3_device_sm_count() * 16;
+    if (blocks > resident) blocks = resident;
+    return (int)q3_launch(kernel, dim3((unsigned)blocks), dim3(256), 0, stream, args...);
 }
 
 }  // namespace
@@ -429,18 +454,23 @@ __global__ void head_gate_kernel(T* __restrict__ x, const T* __restrict__ gate, 
                                         void* first, int save, float lambda, int64_t n_tokens, void* stream) {        \
         if (n_tokens <= 0) return 0;                                                                                  \
         if (width <= 0 || v_off < 0 || v_off + width > row) return Q3_ERR_BAD_SIZE;                                   \
-        const int64_t blocks = (n_tokens * width + 255) / 256;                                                        \
-        return (int)q3_launch(value_mix_kernel<T>, dim3((unsigned)(blocks < 65536 ? blocks : 65536)), dim3(256), 0,   \
-                              (cudaStream_t)stream, (T*)rows, row, v_off, width, bias, (T*)first, save, lambda,       \
-                              n_tokens);                                                                              \
+        constexpr int V = Pack<T>::N;                                                                                 \
+        if (width % V == 0 && row % V == 0 && v_off % V == 0 && aligned16(rows) && aligned16(first))                  \
+            return launch_flat(value_mix_kernel<T, V>, n_tokens * (width / V), (cudaStream_t)stream, (T*)rows, row,   \
+                               v_off, width, bias, (T*)first, save, lambda, n_tokens);                                \
+        return launch_flat(value_mix_kernel<T, 1>, n_tokens * width, (cudaStream_t)stream, (T*)rows, row, v_off,      \
+                           width, bias, (T*)first, save, lambda, n_tokens);                                           \
     }                                                                                                                 \
     Q3_EXPORT int q3_head_gate_##SUFFIX(void* x, const void* gate, int64_t gate_row, int heads, int vd,               \
                                         int64_t n_tokens, void* stream) {                                             \
         if (n_tokens <= 0) return 0;                                                                                  \
         if (heads <= 0 || vd <= 0) return Q3_ERR_BAD_SIZE;                                                            \
-        const int64_t blocks = (n_tokens * heads * vd + 255) / 256;                                                   \
-        return (int)q3_launch(head_gate_kernel<T>, dim3((unsigned)(blocks < 65536 ? blocks : 65536)), dim3(256), 0,   \
-                              (cudaStream_t)stream, (T*)x, (const T*)gate, gate_row, heads, vd, n_tokens);            \
+        constexpr int V = Pack<T>::N;                                                                                 \
+        if (vd % V == 0 && aligned16(x))                                                                              \
+            return launch_flat(head_gate_kernel<T, V>, n_tokens * heads * (vd / V), (cudaStream_t)stream, (T*)x,      \
+                               (const T*)gate, gate_row, heads, vd, n_tokens);                                        \
+        return launch_flat(head_gate_kernel<T, 1>, n_tokens * heads * vd, (cudaStream_t)stream, (T*)x,                \
+                           (const T*)gate, gate_row, heads, vd, n_tokens);                                            \
     }
 
 Q3_ATTENTION_EXPORTS(f32, float)

@@ -292,21 +292,42 @@ static int clamped_mul_launch(const T* gate_up, T* out, int64_t rows, int inter,
                           interleaved, limit, alpha);
 }
 
-template <typename T>
+// VEC values a thread (16 bytes where the sizes allow it, else one).
+template <typename T, int VEC>
 __global__ void scaled_sum_kernel(const T* a, const T* b, float sa, float sb, T* out, int64_t n) {
     pdl_launch_dependents();
     pdl_wait();
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
-        out[i] = from_f32<T>(sa * to_f32<T>(a[i]) + sb * to_f32<T>(b[i]));
+    for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC; i < n; i += (int64_t)gridDim.x * blockDim.x * VEC) {
+        float x[VEC], y[VEC];
+        load_vec<T, VEC>(a + i, x);
+        load_vec<T, VEC>(b + i, y);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) x[k] = sa * x[k] + sb * y[k];
+        store_vec<T, VEC>(out + i, x);
+    }
 }
 
-template <typename T>
+template <typename T, int VEC>
 __global__ void add_bias_kernel(T* x, const float* __restrict__ bias, int64_t rows, int size) {
     pdl_launch_dependents();
     pdl_wait();
     const int64_t n = rows * size;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
-        x[i] = from_f32<T>(to_f32<T>(x[i]) + bias[i % size]);
+    for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC; i < n; i += (int64_t)gridDim.x * blockDim.x * VEC) {
+        float v[VEC];
+        load_vec<T, VEC>(x + i, v);
+        const int c = (int)(i % size);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) v[k] += bias[c + k];
+        store_vec<T, VEC>(x + i, v);
+    }
+}
+
+template <typename Kernel, typename... Args>
+static int launch_flat(Kernel kernel, int64_t work, cudaStream_t stream, Args... args) {
+    int64_t blocks = (work + 255) / 256;
+    const int64_t resident = (int64_t)q3_device_sm_count() * 16;
+    if (blocks > resident) blocks = resident;
+    return (int)q3_launch(kernel, dim3((unsigned)blocks), dim3(256), 0, stream, args...);
 }
 
 // ---------------------------------------------------------------- gather rows (+ pending branch)
@@ -400,15 +421,20 @@ Q3_EXPORT int q3_place_rows(const void* src, int src_kind, void* dst, int dst_ki
     Q3_EXPORT int q3_scaled_sum_##SUFFIX(const void* a, const void* b, float sa, float sb, void* out, int64_t n,    \
                                          void* stream) {                                                            \
         if (n <= 0) return 0;                                                                                       \
-        const int64_t blocks = (n + 255) / 256;                                                                     \
-        return (int)q3_launch(scaled_sum_kernel<T>, dim3((unsigned)(blocks < 65536 ? blocks : 65536)), dim3(256), 0, \
-                              (cudaStream_t)stream, (const T*)a, (const T*)b, sa, sb, (T*)out, n);                  \
+        constexpr int V = Pack<T>::N;                                                                               \
+        if (n % V == 0 && aligned16(a) && aligned16(b) && aligned16(out))                                           \
+            return launch_flat(scaled_sum_kernel<T, V>, n / V, (cudaStream_t)stream, (const T*)a, (const T*)b, sa,  \
+                               sb, (T*)out, n);                                                                     \
+        return launch_flat(scaled_sum_kernel<T, 1>, n, (cudaStream_t)stream, (const T*)a, (const T*)b, sa, sb,      \
+                           (T*)out, n);                                                                             \
     }                                                                                                               \
     Q3_EXPORT int q3_add_bias_##SUFFIX(void* x, const float* bias, int64_t rows, int size, void* stream) {          \
         if (rows <= 0 || size <= 0) return 0;                                                                       \
-        const int64_t blocks = (rows * size + 255) / 256;                                                           \
-        return (int)q3_launch(add_bias_kernel<T>, dim3((unsigned)(blocks < 65536 ? blocks : 65536)), dim3(256), 0,  \
-                              (cudaStream_t)stream, (T*)x, bias, rows, size);                                       \
+        constexpr int V = Pack<T>::N;                                                                               \
+        if (size % V == 0 && aligned16(x))                                                                          \
+            return launch_flat(add_bias_kernel<T, V>, rows * size / V, (cudaStream_t)stream, (T*)x, bias, rows,     \
+                               size);                                                                               \
+        return launch_flat(add_bias_kernel<T, 1>, rows * size, (cudaStream_t)stream, (T*)x, bias, rows, size);      \
     }                                                                                                               \
     Q3_EXPORT int q3_gather_rows_##SUFFIX(const void* x, const void* delta, const int* idx, void* out, int64_t rows, \
                                           int size, void* stream) {                                                 \

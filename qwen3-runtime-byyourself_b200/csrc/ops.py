@@ -503,10 +503,11 @@ def head_gate(x: torch.Tensor, gate: torch.Tensor, heads: int, vd: int) -> torch
 
 def short_conv(u: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, token_seq, seq_start, seq_slots, out: torch.Tensor,
                n_seqs: int) -> torch.Tensor:
-    """Causal convolution over time on the first C columns of u [N, >= C]: out[t, c] = sum_j weight[c, j] u[t - taps + 1 + j, c]
+    """Causal convolution over time on the first C columns of u [N, >= C]: out[t, c] = sum_j weight[j, c] u[t - taps + 1 + j, c]
     within every sequence, the rows before the step from `state` (a view [slots, (taps - 1) * C] of float32 rows, the
-    oldest row first), which is moved on afterwards.  weight float32 [C, taps]; out [N, C] in u's type."""
-    N, (C, taps) = u.shape[0], weight.shape
+    oldest row first), which is moved on afterwards.  weight float32 [taps, C] (a checkpoint's [C, taps] transposed);
+    out [N, C] in u's type."""
+    N, (taps, C) = u.shape[0], weight.shape
     if out.shape != (N, C) or out.dtype != u.dtype or u.shape[1] < C or u.stride(1) != 1 or state.shape[1] != (taps - 1) * C \
             or state.dtype != torch.float32 or (taps > 1 and state.stride(1) != 1) or not out.is_contiguous() or out.data_ptr() == u.data_ptr():
         raise KernelError("short_conv: shapes do not fit")

@@ -10,31 +10,56 @@
 //   short_conv_state : afterwards, one thread per (sequence, channel) moves the state on: the last taps - 1 rows of
 //                      (old state, the step's rows).
 //
-// u has `row_in` values per row (the convolved channels are its first C), y is dense [N, C]; w float32 [C, taps].
+// u has `row_in` values per row (the convolved channels are its first C), y is dense [N, C]; w float32 [taps, C] (tap
+// by tap, so that neighbouring channels' weights are neighbours).
 #include "common.cuh"
 
 namespace {
 
-template <typename T>
+// VEC channels a thread (16 bytes of a row where the sizes allow it, else one).
+template <typename T, int VEC>
 __global__ void short_conv_kernel(const T* __restrict__ u, int64_t row_in, const float* __restrict__ w, const float* __restrict__ state,
                                   int64_t slot_stride, const int* __restrict__ token_seq, const int* __restrict__ seq_start,
                                   const int* __restrict__ seq_slots, T* __restrict__ y, int C, int taps, int64_t n_tokens) {
     pdl_launch_dependents();
     pdl_wait();
-    const int64_t total = n_tokens * C;
+    const int per_row = C / VEC;
+    const int64_t total = n_tokens * per_row;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t t = i / C;
-        const int c = (int)(i % C);
+        const int64_t t = i / per_row;
+        const int c = (int)(i % per_row) * VEC;
         const int seq = token_seq[t];
         const int64_t first = seq_start[seq];                  // the step's first row of this sequence
         const float* st = state + (int64_t)seq_slots[seq] * slot_stride;
-        float acc = 0.0f;
+        float acc[VEC];
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) acc[k] = 0.0f;
         for (int j = 0; j < taps; ++j) {
             const int64_t src = t - (taps - 1) + j;
-            const float x = src >= first ? to_f32<T>(u[src * row_in + c]) : st[(int64_t)(taps - 1 + (src - first)) * C + c];
-            acc = fmaf(w[(int64_t)c * taps + j], x, acc);
+            float x[VEC];
+            if (src >= first) {
+                if constexpr (VEC == 1) {
+                    x[0] = to_f32<T>(u[src * row_in + c]);
+                } else {
+                    const Pack<T> pk = load_pack<T>(u + src * row_in + c);
+#pragma unroll
+                    for (int k = 0; k < VEC; ++k) x[k] = pk.get(k);
+                }
+            } else {
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) x[k] = st[(int64_t)(taps - 1 + (src - first)) * C + c + k];
+            }
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) acc[k] = fmaf(w[(int64_t)j * C + c + k], x[k], acc[k]);
         }
-        y[i] = from_f32<T>(acc);
+        if constexpr (VEC == 1) {
+            y[t * C + c] = from_f32<T>(acc[0]);
+        } else {
+            Pack<T> pk;
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) pk.set(k, acc[k]);
+            store_pack<T>(y + t * C + c, pk);
+        }
     }
 }
 
@@ -66,10 +91,16 @@ __global__ void short_conv_state_kernel(const T* __restrict__ u, int64_t row_in,
                                          int channels, int taps, int64_t n_tokens, int n_seqs, void* stream) {           \
         if (n_tokens <= 0 || n_seqs <= 0) return 0;                                                                       \
         if (channels <= 0 || taps <= 0 || taps > 64 || row_in < channels) return Q3_ERR_BAD_SIZE;                         \
-        const int64_t blocks = (n_tokens * channels + 255) / 256;                                                         \
-        int code = (int)q3_launch(short_conv_kernel<T>, dim3((unsigned)(blocks < 65536 ? blocks : 65536)), dim3(256), 0,  \
-                                  (cudaStream_t)stream, (const T*)u, row_in, w, (const float*)state, slot_stride,         \
-                                  token_seq, seq_start, seq_slots, (T*)y, channels, taps, n_tokens);                      \
+        constexpr int V = Pack<T>::N;                                                                                     \
+        const bool vec = channels % V == 0 && row_in % V == 0 && aligned16(u) && aligned16(y);                            \
+        const int64_t blocks = (n_tokens * (channels / (vec ? V : 1)) + 255) / 256;                                       \
+        const dim3 grid((unsigned)(blocks < 65536 ? blocks : 65536));                                                     \
+        int code = vec ? (int)q3_launch(short_conv_kernel<T, V>, grid, dim3(256), 0, (cudaStream_t)stream, (const T*)u,   \
+                                        row_in, w, (const float*)state, slot_stride, token_seq, seq_start, seq_slots,    \
+                                        (T*)y, channels, taps, n_tokens)                                                  \
+                       : (int)q3_launch(short_conv_kernel<T, 1>, grid, dim3(256), 0, (cudaStream_t)stream, (const T*)u,   \
+                                        row_in, w, (const float*)state, slot_stride, token_seq, seq_start, seq_slots,    \
+                                        (T*)y, channels, taps, n_tokens);                                                 \
         if (code != 0 || taps == 1) return code;                                                                          \
         const int64_t sblocks = ((int64_t)n_seqs * channels + 255) / 256;                                                 \
         return (int)q3_launch(short_conv_state_kernel<T>, dim3((unsigned)(sblocks < 65536 ? sblocks : 65536)), dim3(256), \

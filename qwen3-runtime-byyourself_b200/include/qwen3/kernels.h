@@ -341,7 +341,7 @@ int q3_head_gate_f32(void* x, const void* gate, int64_t gate_row, int heads, int
 int q3_head_gate_bf16(void* x, const void* gate, int64_t gate_row, int heads, int vd, int64_t n_tokens, void* stream);
 
 /* ---- short_conv.cu ------------------------------------------------------------------------------------------- */
-/* y[t, c] = sum_j w[c, j] u[t - taps + 1 + j, c] within every sequence; rows before the step come from state
+/* y[t, c] = sum_j w[j, c] u[t - taps + 1 + j, c] (w [taps, channels]) within every sequence; rows before the step come from state
    [slot][taps - 1][channels] (float32), which is moved on afterwards */
 int q3_short_conv_f32(const void* u, int64_t row_in, const float* w, float* state, int64_t slot_stride, const int* token_seq,
                       const int* seq_start, const int* seq_slots, void* y, int channels, int taps, int64_t n_tokens, int n_seqs,

@@ -176,6 +176,8 @@ class GQAAttention(Part):
             if self.conv_weight is not None:
                 self.conv_weight[:rows.numel()] = self.conv_weight[:rows.numel()][rows]
             self.reordered = True
+        if self.conv_weight is not None:
+            self.conv_weight = self.conv_weight.t().contiguous()        # [taps, channels], as the kernel reads it
         if self.q_norm is not None:
             self.q_norm.bind(weights, p + n["q_norm"], dtype, device)
             self.k_norm.bind(weights, p + n["k_norm"], dtype, device)

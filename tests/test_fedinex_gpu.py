@@ -186,7 +186,7 @@ def test_short_convolution_carries_its_last_rows_from_step_to_step(dtype, channe
         N = int(start[-1])
         u = dev(rng.standard_normal((N, channels + 3)), T)                 # three more columns that are not convolved
         out = torch.full((N, channels), 9.0, dtype=T, device="cuda")
-        ops.short_conv(u, w, state, dev(seq, torch.int32), dev(start, torch.int32), dev([s for s, _ in live], torch.int32), out, len(live))
+        ops.short_conv(u, w.t().contiguous(), state, dev(seq, torch.int32), dev(start, torch.int32), dev([s for s, _ in live], torch.int32), out, len(live))
         for i, (slot, n) in enumerate(live):
             old = len(history[slot])
             history[slot] = np.concatenate([history[slot], f64(u)[start[i]:start[i + 1], :channels]])
@@ -580,6 +580,25 @@ def test_a_long_decode_gives_pages_back_but_for_the_kept_ones_and_a_reused_slot_
         engine.release(slot)
         err = max(float(np.max(np.abs(r - exact[99 + i]))) for i, r in enumerate(rows))
         assert err <= FP32_TOL * max(1.0, scale), (round_, err)
+
+
+@pytest.mark.parametrize("kind", ["gla", "parallel", "attention", "one_tap"])
+def test_models_of_one_kind_of_layer(tmp_path, kind):
+    """No page group at all (only recurrences), only layers with pages and state, only windowed attention without blended
+    values, and a convolution of one tap (no rows to carry): prompt, then token by token, in 32-bit."""
+    mixers = {"gla": [gla(2, 8, 12, 5.0, 4), gla(1, 16, 8, 9.0, 2)],
+              "parallel": [parallel(conv_attention(2, 1, 8, 8, 0.3, 1000.0, 4, conv=2), memory(2, 8, 8, 5.0), 0.5, 0.5)] * 2,
+              "attention": [attention(2, 1, 8, 12, 0.3, 100.0, 8, window=20, keep_first=2), attention(4, 4, 8, 8, 0.3)],
+              "one_tap": [parallel(conv_attention(2, 2, 8, 8, 0.3, conv=1), memory(1, 8, 8, 3.0), 1.0, -1.0)]}[kind]
+    cfg = {"architecture": "Fedinex", "vocab": 80, "width": 40, "norm": {"eps": 1e-5},
+           "layers": [layer(m, dense(48, 2.0) if i % 2 else moe_spec(16, 2.0, 4, 2, 1.5, groups=(2, 1))) for i, m in enumerate(mixers)]}
+    folder, weights = make_folder(tmp_path, cfg, seed=12)
+    requests = make_requests(cfg, [90, 3], seed=13)
+    steps, rows = schedules.tail_one_by_one(requests, 40)
+    engine = engine_for(folder, "float32", schedules.peak_tokens(steps))
+    got = run_steps(engine, steps, rows)
+    check(got, requests, "one kind: " + kind, weights, "float32", "one kind", cfg=cfg)
+    assert engine.cache.pages_held() == 0
 
 
 @pytest.mark.parametrize("name", ["A", "C", "D"])
