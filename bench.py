@@ -493,14 +493,14 @@ def fedinex_config(width, heads, kv, d, ff, layers, window=1024, keep_first=4, e
     so on.  The first layer's feed-forward is dense, the others routed (`experts` experts of ff / (2 top), `top` per token,
     four groups of which two are kept)."""
     rot = {"base": 1000000.0, "dims": d // 2}
-    linear = {"type": "gla", "mixer": {"heads": width // d, "dim": d, "vdim": d, "tau": 16.0, "rank": 64}}
+    linear = {"type": "gla", "mixer": {"heads": width // d, "dim": d, "vdim": d, "tau": 8.0, "rank": 64}}
     windowed = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv, "dim": d, "vdim": d, "scale": d ** -0.5, "rot": rot,
                                                 "mask": {"size": window, "keep_first": keep_first}, "v_mix": True}}
     both = {"type": "parallel", "mixer": {"left": {"heads": heads, "kv_heads": kv, "dim": d, "vdim": d, "scale": d ** -0.5, "rot": rot, "conv": 4},
-                                           "right": {"heads": max(width // (2 * d), 1), "dim": d, "vdim": d, "gate_cap": 15.0},
-                                           "left_scale": 0.6, "right_scale": 0.9}}
+                                           "right": {"heads": max(width // (2 * d), 1), "dim": d, "vdim": d, "gate_cap": 10.0},
+                                           "left_scale": 0.5, "right_scale": 1.0}}
     moe = {"kind": "moe", "expert": {"ff": ff // (2 * top), "limit": 7.0},
-           "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+           "router": {"experts": experts, "top": top, "scale": 2.0, "groups": {"count": 4, "keep": 2}}}
     order = [linear, windowed, both, windowed]
     return {"architecture": "Fedinex", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-6},
             "layers": [dict(order[i % 4], mlp={"kind": "dense", "ff": ff, "limit": 7.0} if i == 0 else moe) for i in range(layers)]}

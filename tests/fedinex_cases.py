@@ -62,7 +62,7 @@ E_A = {
     "layers": [layer(gla(3, 8, 12, 8.0, 6), dense(96, 1.2)),
                layer(attention(4, 2, 16, 24, 0.3, 10000.0, 8, window=70, keep_first=5, v_mix=True), moe(40, 1.5, 6, 3, 1.7, groups=(3, 2))),
                layer(parallel(conv_attention(4, 1, 16, 24, 0.2, 500.0, 6, conv=4), memory(3, 8, 12, 6.0), 0.7, 1.1), dense(72, 2.0)),
-               layer(attention(2, 2, 32, 24, 0.2, 1e6, 32, window=33, keep_first=1, v_mix=True), None),
+               layer(attention(2, 2, 32, 24, 0.2, 7e5, 32, window=33, keep_first=1, v_mix=True), None),
                layer(attention(6, 2, 8, 24, 0.4, window=9, keep_first=9, v_mix=True), moe(24, 3.0, 4, 1, 0.5))],
 }
 # The order the other way round; a window of exactly one page without kept keys; attention without rotation, without
@@ -70,9 +70,9 @@ E_A = {
 # group; the whole head rotated.
 E_B = {
     "architecture": "Fedinex", "vocab": 128, "width": 96, "norm": {"eps": 1e-5},
-    "layers": [layer(parallel(conv_attention(1, 1, 32, 32, 0.18, 250.0, 32, conv=2), memory(1, 64, 48, 15.0), 1.0, 1.0), moe(48, 2.0, 1, 1, 1.0)),
+    "layers": [layer(parallel(conv_attention(1, 1, 32, 32, 0.18, 250.0, 32, conv=2), memory(1, 64, 48, 10.0), 1.0, 1.0), moe(48, 2.25, 1, 1, 1.0)),
                layer(attention(2, 2, 16, 16, 0.25, window=64), dense(160, 7.0)),
-               layer(gla(1, 64, 128, 16.0, 16), moe(32, 1.0, 8, 8, 2.5, groups=(1, 1))),
+               layer(gla(1, 64, 128, 20.0, 8), moe(32, 1.0, 8, 8, 1.25, groups=(1, 1))),
                layer(parallel(conv_attention(2, 1, 16, 8, 0.25), memory(2, 16, 16, 4.0), -0.5, 2.0), dense(64, 0.8)),
                layer(attention(3, 1, 32, 16, 0.2, 50000.0, 16), moe(64, 2.0, 6, 2, 3.0, groups=(2, 1)))],
 }
@@ -80,10 +80,10 @@ E_B = {
 # state of 128 x 128; groups of four experts.
 E_C = {
     "architecture": "Fedinex", "vocab": 320, "width": 128, "norm": {"eps": 1e-5},
-    "layers": [layer(attention(4, 2, 64, 64, 0.125, 1e6, 32, window=150, keep_first=70, v_mix=True), moe(64, 2.0, 8, 2, 2.0, groups=(2, 1))),
-               layer(gla(2, 128, 128, 16.0, 16), dense(256, 1.5)),
-               layer(parallel(conv_attention(8, 2, 64, 64, 0.125, 250000.0, 32, conv=3), memory(2, 128, 64, 15.0), 0.6, 0.9), moe(96, 2.0, 8, 4, 2.5, groups=(4, 2))),
-               layer(attention(2, 2, 128, 64, 0.09, 10000.0, 128, window=200, keep_first=3, v_mix=True), dense(128, 1.5))],
+    "layers": [layer(attention(4, 2, 64, 64, 0.14, 5e5, 32, window=150, keep_first=70, v_mix=True), moe(64, 1.75, 8, 2, 2.0, groups=(2, 1))),
+               layer(gla(2, 128, 128, 12.0, 24), dense(256, 1.25)),
+               layer(parallel(conv_attention(8, 4, 64, 64, 0.11, 300000.0, 48, conv=3), memory(2, 128, 64, 12.0), 0.8, 0.7), moe(80, 2.5, 8, 4, 3.0, groups=(4, 2))),
+               layer(attention(2, 2, 128, 64, 0.09, 10000.0, 128, window=200, keep_first=3, v_mix=True), dense(128, 1.75))],
 }
 # Sizes that rule out every vector path: a width that is no multiple of 4, odd head sizes and vocabulary; a window of one
 # position (a token sees itself and the kept keys only); two rotated values; every expert chosen; pairs of experts as
@@ -91,7 +91,7 @@ E_C = {
 E_D = {
     "architecture": "Fedinex", "vocab": 97, "width": 50, "norm": {"eps": 1e-5},
     "layers": [layer(gla(3, 5, 9, 3.0, 3), moe(21, 1.0, 4, 4, 1.5, groups=(2, 2))),
-               layer(attention(3, 3, 6, 9, 0.3, 100.0, 2, window=1, keep_first=2, v_mix=True), dense(30, 1.5)),
+               layer(attention(3, 3, 6, 9, 0.3, 100.0, 2, window=1, keep_first=2, v_mix=True), dense(30, 1.4)),
                layer(parallel(conv_attention(2, 1, 5, 7, 0.4, 30.0, 4, conv=5), memory(1, 11, 3, 2.5), 0.3, 1.4), None),
                layer(attention(3, 3, 11, 9, 0.3, 1000.0, 10, window=7, v_mix=True), moe(12, 2.5, 6, 3, 1.0, groups=(3, 2)))],
 }

@@ -127,8 +127,8 @@ def test_a_size_the_file_does_not_give_comes_from_the_checkpoint(tmp_path):
 def test_the_book_keeps_the_pages_of_the_first_keys_of_a_window_group():
     from qwen3_b200.cache import CacheBook, CacheNeed
     page = 64
-    needs = [CacheNeed("window", 1, 8, window=40, keep_first=70), CacheNeed("window", 1, 8, window=40),
-             CacheNeed("window", 1, 8, window=40, keep_first=1), CacheNeed("full", 1, 8)]
+    needs = [CacheNeed("window", 1, 8, window=45, keep_first=70), CacheNeed("window", 1, 8, window=45),
+             CacheNeed("window", 1, 8, window=45, keep_first=1), CacheNeed("full", 1, 8)]
     book = CacheBook(needs, max_tokens=10 * page, max_seq_len=10 * page, n_slots=2)
     assert len(book.groups) == 4                                    # the kept stretch is part of what a group is
     slot = book.alloc_slot()

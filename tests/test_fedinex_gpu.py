@@ -260,7 +260,7 @@ def test_router_with_sigmoid_scores_and_groups_marked_by_their_two_best(dtype, e
     import torch
     from qwen3_b200.csrc import ops
     rng = np.random.default_rng(experts * 10 + top)
-    T, N, hidden, scale = torch_dtype(dtype), 200, 40, 2.5
+    T, N, hidden, scale = torch_dtype(dtype), 200, 40, 1.75
     h = dev(rng.standard_normal((N, hidden)), T)
     w = dev(rng.standard_normal((experts, hidden)) * 0.6, T)
     correction = rng.standard_normal(experts) * 0.4 - 0.3                # some choice scores are negative
@@ -343,7 +343,7 @@ def check_planted(got, take, seqs, T, window, keep, where, tol):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,G,d,vd,window,keep", [(4, 2, 16, 24, 40, 6), (2, 1, 64, 64, 70, 70), (3, 3, 5, 9, 1, 2), (2, 2, 32, 32, 64, 0),
+@pytest.mark.parametrize("H,G,d,vd,window,keep", [(4, 2, 16, 24, 37, 5), (2, 1, 64, 64, 70, 70), (3, 3, 5, 9, 1, 2), (2, 2, 32, 32, 64, 0),
                                                   (4, 1, 64, 64, 130, 1), (1, 1, 8, 8, 200, 65)])
 @pytest.mark.parametrize("where", sorted(WHERE))
 def test_attention_sees_the_window_and_the_kept_keys_and_nothing_between(dtype, H, G, d, vd, window, keep, where):
@@ -368,7 +368,7 @@ def test_attention_sees_the_window_and_the_kept_keys_and_nothing_between(dtype, 
     check_planted(f64(out).reshape(N, H, vd), take, seqs, T, window, keep, where, 2e-5 if dtype == "float32" else 3e-2)
 
 
-@pytest.mark.parametrize("H,G,d,vd,window,keep", [(4, 2, 16, 32, 40, 6), (2, 1, 64, 64, 70, 70), (2, 2, 32, 32, 64, 0), (4, 1, 64, 64, 130, 1),
+@pytest.mark.parametrize("H,G,d,vd,window,keep", [(4, 2, 16, 32, 37, 5), (2, 1, 64, 64, 70, 70), (2, 2, 32, 32, 64, 0), (4, 1, 64, 64, 130, 1),
                                                   (2, 1, 128, 64, 200, 65), (16, 1, 16, 16, 1, 2), (2, 2, 64, 64, 63, 129)])
 @pytest.mark.parametrize("where", sorted(WHERE))
 def test_tiled_attention_kernels_walk_the_kept_pages_before_the_window_s(H, G, d, vd, window, keep, where):
