@@ -582,22 +582,25 @@ def test_a_long_decode_gives_pages_back_but_for_the_kept_ones_and_a_reused_slot_
         assert err <= FP32_TOL * max(1.0, scale), (round_, err)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("kind", ["gla", "parallel", "attention", "one_tap"])
-def test_models_of_one_kind_of_layer(tmp_path, kind):
-    """No page group at all (only recurrences), only layers with pages and state, only windowed attention without blended
-    values, and a convolution of one tap (no rows to carry): prompt, then token by token, in 32-bit."""
+def test_models_of_one_kind_of_layer(tmp_path, kind, dtype):
+    """No page group at all (only recurrences), only layers with pages and state, only attention (blended values with and
+    without a window, head sizes the tiled kernels take), and a convolution of one tap (no rows to carry): prompt, then token
+    by token."""
     mixers = {"gla": [gla(2, 8, 12, 5.0, 4), gla(1, 16, 8, 9.0, 2)],
               "parallel": [parallel(conv_attention(2, 1, 8, 8, 0.3, 1000.0, 4, conv=2), memory(2, 8, 8, 5.0), 0.5, 0.5)] * 2,
-              "attention": [attention(2, 1, 8, 12, 0.3, 100.0, 8, window=20, keep_first=2), attention(4, 4, 8, 8, 0.3)],
+              "attention": [attention(2, 2, 16, 16, 0.3, 100.0, 8, v_mix=True), attention(4, 2, 16, 16, 0.3, window=20, keep_first=2, v_mix=True),
+                            attention(2, 2, 32, 16, 0.2, 3000.0, 32, v_mix=True)],
               "one_tap": [parallel(conv_attention(2, 2, 8, 8, 0.3, conv=1), memory(1, 8, 8, 3.0), 1.0, -1.0)]}[kind]
     cfg = {"architecture": "Fedinex", "vocab": 80, "width": 40, "norm": {"eps": 1e-5},
            "layers": [layer(m, dense(48, 2.0) if i % 2 else moe_spec(16, 2.0, 4, 2, 1.5, groups=(2, 1))) for i, m in enumerate(mixers)]}
-    folder, weights = make_folder(tmp_path, cfg, seed=12)
+    folder, weights = make_folder(tmp_path, cfg, seed=12, decided=dtype == "bfloat16")
     requests = make_requests(cfg, [90, 3], seed=13)
     steps, rows = schedules.tail_one_by_one(requests, 40)
-    engine = engine_for(folder, "float32", schedules.peak_tokens(steps))
+    engine = engine_for(folder, dtype, schedules.peak_tokens(steps))
     got = run_steps(engine, steps, rows)
-    check(got, requests, "one kind: " + kind, weights, "float32", "one kind", cfg=cfg)
+    check(got, requests, "one kind: " + kind, weights, dtype, "one kind", cfg=cfg)
     assert engine.cache.pages_held() == 0
 
 
