@@ -233,7 +233,8 @@ class GQAAttention(Part):
             linear(x, self.w_qkv, raw)
             if self.conv_taps > 1 and cache.state is None:
                 raise ops.KernelError("the short convolution keeps rows per sequence: the cache was built without its state")
-            state = cache.state.view(cache.state.shape[0], -1) if cache.state is not None else raw.new_zeros((1, 0), dtype=torch.float32)
+            # one tap carries no rows from step to step: the kernel then gets rows of no values
+            state = cache.state.view(cache.state.shape[0], -1) if cache.state is not None else ctx.scratch.get("attn.no_state", (1, 0), torch.float32)
             ops.short_conv(raw, self.conv_weight, state, ctx.token_seq, ctx.seq_start, ctx.seq_slots, qkv, ctx.n_seqs)
         else:
             linear(x, self.w_qkv, qkv)
