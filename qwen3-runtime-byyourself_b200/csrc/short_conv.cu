@@ -3,8 +3,9 @@
 //
 //     y[t, c] = sum_j w[c, j] * u[t - taps + 1 + j, c],   j = 0 .. taps - 1,   u = 0 before the sequence's start
 //
-//   short_conv       : one thread per (token, channel); an input row before the step's first token comes from the
-//                      state [slot][taps - 1][C] (float32; the oldest row first), which holds zeros for a new sequence.
+//   short_conv       : one thread per (token, channel) - or, for 2 to 4 taps and rows of 16-byte packets, per run of up to 16
+//                      tokens and packet of channels, the last rows kept in registers; an input row before the step's first
+//                      token comes from the state [slot][taps - 1][C] (float32; the oldest row first), zeros for a new sequence.
 //                      The products are summed in 32-bit in ascending j whatever the step, so a token's output is the
 //                      same bits however the sequence was cut.
 //   short_conv_state : afterwards, one thread per (sequence, channel) moves the state on: the last taps - 1 rows of
@@ -63,6 +64,84 @@ __global__ void short_conv_kernel(const T* __restrict__ u, int64_t row_in, const
     }
 }
 
+// The same for TAPS known at compile time and 16-byte packets: a thread walks `run` consecutive tokens of its VEC channels
+// with the last TAPS - 1 rows in registers, so that every row is read once (and TAPS - 1 more at the start of a run or of a
+// sequence).  The sums run in the same order as above: the same bits.
+template <typename T, int VEC, int TAPS>
+__global__ void short_conv_walk_kernel(const T* __restrict__ u, int64_t row_in, const float* __restrict__ w, const float* __restrict__ state,
+                                       int64_t slot_stride, const int* __restrict__ token_seq, const int* __restrict__ seq_start,
+                                       const int* __restrict__ seq_slots, T* __restrict__ y, int C, int64_t n_tokens, int run) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+    if (c >= C) return;
+    float wt[TAPS][VEC], win[TAPS > 1 ? TAPS - 1 : 1][VEC];
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j)
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) wt[j][k] = w[(int64_t)j * C + c + k];
+    const int64_t t_begin = (int64_t)blockIdx.y * run, t_end = min(t_begin + run, n_tokens);
+    int cur = -1;
+    for (int64_t t = t_begin; t < t_end; ++t) {
+        const int seq = token_seq[t];
+        if (seq != cur) {                                      // the run's first token, or a sequence's first: fill the window
+            cur = seq;
+            const int64_t first = seq_start[seq];
+            const float* st = state + (int64_t)seq_slots[seq] * slot_stride;
+#pragma unroll
+            for (int j = 0; j < TAPS - 1; ++j) {
+                const int64_t src = t - (TAPS - 1) + j;
+                if (src >= first) {
+                    const Pack<T> pk = load_pack<T>(u + src * row_in + c);
+#pragma unroll
+                    for (int k = 0; k < VEC; ++k) win[j][k] = pk.get(k);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < VEC; ++k) win[j][k] = st[(int64_t)(TAPS - 1 + (src - first)) * C + c + k];
+                }
+            }
+        }
+        const Pack<T> pk = load_pack<T>(u + t * row_in + c);
+        float x[VEC], acc[VEC];
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+            x[k] = pk.get(k);
+            acc[k] = 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < TAPS - 1; ++j)
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) acc[k] = fmaf(wt[j][k], win[j][k], acc[k]);
+        Pack<T> out;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+            acc[k] = fmaf(wt[TAPS - 1][k], x[k], acc[k]);
+            out.set(k, acc[k]);
+        }
+        store_pack<T>(y + t * C + c, out);
+#pragma unroll
+        for (int j = 0; j + 1 < TAPS - 1; ++j)
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) win[j][k] = win[j + 1][k];
+        if (TAPS > 1) {
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) win[TAPS - 2 > 0 ? TAPS - 2 : 0][k] = x[k];
+        }
+    }
+}
+
+template <typename T, int TAPS>
+int short_conv_walk_launch(const T* u, int64_t row_in, const float* w, const float* state, int64_t slot_stride, const int* token_seq,
+                           const int* seq_start, const int* seq_slots, T* y, int C, int64_t n_tokens, cudaStream_t stream) {
+    constexpr int V = Pack<T>::N;
+    const int run = n_tokens >= 1024 ? 16 : (n_tokens >= 128 ? 4 : 1);
+    const int64_t runs = (n_tokens + run - 1) / run;
+    if (runs > 65535) return Q3_ERR_TOO_LARGE;
+    const dim3 grid((unsigned)((C / V + 127) / 128), (unsigned)runs);
+    return (int)q3_launch(short_conv_walk_kernel<T, V, TAPS>, grid, dim3(128), 0, stream, u, row_in, w, state, slot_stride, token_seq,
+                          seq_start, seq_slots, y, C, n_tokens, run);
+}
+
 template <typename T>
 __global__ void short_conv_state_kernel(const T* __restrict__ u, int64_t row_in, float* __restrict__ state, int64_t slot_stride,
                                         const int* __restrict__ seq_start, const int* __restrict__ seq_slots, int C, int taps,
@@ -95,7 +174,17 @@ __global__ void short_conv_state_kernel(const T* __restrict__ u, int64_t row_in,
         const bool vec = channels % V == 0 && row_in % V == 0 && aligned16(u) && aligned16(y);                            \
         const int64_t blocks = (n_tokens * (channels / (vec ? V : 1)) + 255) / 256;                                       \
         const dim3 grid((unsigned)(blocks < 65536 ? blocks : 65536));                                                     \
-        int code = vec ? (int)q3_launch(short_conv_kernel<T, V>, grid, dim3(256), 0, (cudaStream_t)stream, (const T*)u,   \
+        const bool walk = vec && taps >= 2 && taps <= 4 && (n_tokens + 15) / 16 <= 65535;                                 \
+        int code = walk ? (taps == 2 ? short_conv_walk_launch<T, 2>((const T*)u, row_in, w, state, slot_stride, token_seq, \
+                                                                    seq_start, seq_slots, (T*)y, channels, n_tokens,      \
+                                                                    (cudaStream_t)stream)                                 \
+                           : taps == 3 ? short_conv_walk_launch<T, 3>((const T*)u, row_in, w, state, slot_stride,         \
+                                                                      token_seq, seq_start, seq_slots, (T*)y, channels,   \
+                                                                      n_tokens, (cudaStream_t)stream)                     \
+                                       : short_conv_walk_launch<T, 4>((const T*)u, row_in, w, state, slot_stride,         \
+                                                                      token_seq, seq_start, seq_slots, (T*)y, channels,   \
+                                                                      n_tokens, (cudaStream_t)stream))                    \
+                   : vec ? (int)q3_launch(short_conv_kernel<T, V>, grid, dim3(256), 0, (cudaStream_t)stream, (const T*)u,   \
                                         row_in, w, (const float*)state, slot_stride, token_seq, seq_start, seq_slots,    \
                                         (T*)y, channels, taps, n_tokens)                                                  \
                        : (int)q3_launch(short_conv_kernel<T, 1>, grid, dim3(256), 0, (cudaStream_t)stream, (const T*)u,   \

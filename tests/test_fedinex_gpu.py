@@ -166,10 +166,13 @@ def test_heads_are_divided_normed_weighted_and_gated(dtype, heads, vd, normalise
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("channels,taps", [(7, 4), (64, 3), (200, 2), (5, 1), (9, 8)])
-def test_short_convolution_carries_its_last_rows_from_step_to_step(dtype, channels, taps):
+@pytest.mark.parametrize("channels,taps,extra", [(7, 4, 3), (64, 3, 3), (200, 2, 3), (5, 1, 3), (9, 8, 3), (64, 3, 8), (200, 2, 0), (16, 4, 16),
+                                                 (64, 5, 8), (8, 1, 8)])
+def test_short_convolution_carries_its_last_rows_from_step_to_step(dtype, channels, taps, extra):
     """Steps of whole prompts, of portions shorter than the taps, and of single tokens: every output row is what the
-    whole sequence gives, and the state ends as the last taps - 1 rows."""
+    whole sequence gives, and the state ends as the last taps - 1 rows.  `extra` columns that are not convolved follow the
+    channels: with rows of whole 16-byte packets the kernels that move packets run (for 2 to 4 taps the one that walks runs
+    of tokens, whose runs here start inside, before and after a sequence's start)."""
     import torch
     from qwen3_b200.csrc import ops
     rng = np.random.default_rng(channels)
@@ -180,11 +183,11 @@ def test_short_convolution_carries_its_last_rows_from_step_to_step(dtype, channe
     whole[:, width:] = 5.0
     state = whole[:, :width]
     history = {s: np.zeros((0, channels)) for s in slots}
-    for lengths in ([9, 1, 2], [1, 1, 1], [2, 0, 1], [1, 30, 3], [1, 1, 1]):
+    for lengths in ([9, 1, 2], [1, 1, 1], [2, 0, 1], [1, 30, 3], [1, 1, 1], [70, 3, 131], [1200, 0, 5]):
         live = [(s, n) for s, n in zip(slots, lengths) if n > 0]
         start, seq = packed([n for _, n in live])
         N = int(start[-1])
-        u = dev(rng.standard_normal((N, channels + 3)), T)                 # three more columns that are not convolved
+        u = dev(rng.standard_normal((N, channels + extra)), T)             # more columns that are not convolved
         out = torch.full((N, channels), 9.0, dtype=T, device="cuda")
         ops.short_conv(u, w.t().contiguous(), state, dev(seq, torch.int32), dev(start, torch.int32), dev([s for s, _ in live], torch.int32), out, len(live))
         for i, (slot, n) in enumerate(live):
